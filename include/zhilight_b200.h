@@ -409,7 +409,11 @@ enum {
     ZL_GEMM_EPI_SIGMOID_GATE = 2 /* v * sigmoid(gate) */,
     ZL_GEMM_EPI_TANH = 3,
     ZL_GEMM_EPI_GLU_CLAMP = 4 /* columns 2j, 2j+1 = gate, up -> column j: g = min(gate, limit), u = clamp(up, +-limit),
-                                 g * sigmoid(alpha * g) * (u + beta); grouped call only */
+                                 g * sigmoid(alpha * g) * (u + beta); grouped call only */,
+    ZL_GEMM_EPI_GEGLU_TANH = 5 /* columns 2j, 2j+1 = gate, up -> column j: gelu_tanh(gate) * up, with
+                                  gelu_tanh(z) = z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) */,
+    ZL_GEMM_EPI_GELU_TANH_MUL = 6 /* gelu_tanh(v) * mul[m][n] */,
+    ZL_GEMM_EPI_SOFTCAP = 7 /* limit * tanh(v / limit) */
 };
 /* y[b](M,N) = epi(x[b](M,K) @ w[b](N,K)^T), b < batch, element strides per batch entry; any M, N, K.  in_dtype
  * ZL_F16 / ZL_BF16 (tensor cores, fp32 accumulation) or ZL_F32 (plain fp32 FMAs, no reduced-precision mode);
@@ -421,6 +425,12 @@ int zl_gemm_nt(const void* x, long long ldx, long long x_batch_stride, const voi
 /* One problem with a per-column fp32 bias (NULL: none) added before the epilogue (none, relu^2 or tanh). */
 int zl_gemm_nt_bias(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* y, long long ldy,
                     int M, int N, int K, int in_dtype, int out_dtype, int epilogue, int pdl, zl_stream_t stream);
+/* One problem with a per-column fp32 bias (NULL: none) and any epilogue but the clamped unit: none, relu^2, tanh, sigmoid
+ * gate / gelu_tanh times multiplier (mul fp32 (M, N), row stride ld_mul), gelu_tanh(gate) * up over column pairs (the
+ * bias has N entries, y has N / 2 columns), soft cap at `limit`. */
+int zl_gemm_nt_fused(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* y, long long ldy,
+                     int M, int N, int K, int in_dtype, int out_dtype, int epilogue, const float* mul, long long ld_mul,
+                     float limit, int pdl, zl_stream_t stream);
 /* Grouped problems for mixtures of experts.  A list of rows sorted by group: group g owns the list entries
  * group_offsets[g] .. group_offsets[g+1] (device, groups + 1 ints) and the weight block w + g * w_group_stride (N, K).
  * List entry i reads row x_rows[i] of x (NULL: row i) and writes row y_rows[i] of y (NULL: row i).  max_rows bounds the
@@ -543,10 +553,49 @@ int zl_sink_attention(const void* q, void* const* k_addrs, void* const* v_addrs,
                       int kv_heads, int dim, int vdim, int splits, void* workspace, size_t workspace_bytes,
                       const int32_t* run_row0, const int32_t* run_len, int runs, int max_run_len, int dtype, int pdl,
                       zl_stream_t stream);
+/* The same with two restrictions a design may add.  chunk > 0: token t sees only the keys from (pos[t] / chunk) * chunk
+ * on (blocks of `chunk` positions counted from position 0 of the sequence).  dist_bias != NULL (device, fp32
+ * (heads, n_dist)): dist_bias[h][min(pos[t] - j, n_dist - 1)] is added to the scaled score of key j; the sink gets none.
+ * max_len passed to zl_sink_attention_splits may be the chunk size when chunk > 0. */
+int zl_sink_attention_local(const void* q, void* const* k_addrs, void* const* v_addrs, const int32_t* slot,
+                            const int32_t* pos, const float* sink, const float* gate, long long ldg, float scale, int chunk,
+                            const float* dist_bias, int n_dist, void* out, int T, int heads, int kv_heads, int dim, int vdim,
+                            int splits, void* workspace, size_t workspace_bytes, const int32_t* run_row0,
+                            const int32_t* run_len, int runs, int max_run_len, int dtype, int pdl, zl_stream_t stream);
+/* Host helper: a learned table (rows, heads) indexed by a bucket of the distance n -> out_host (heads, n_dist), entry
+ * [h][n] = table[bucket(n)][h] with bucket(n) = n below half = rows / 2 and
+ * min(rows - 1, half + floor(ln(n / half) / ln(far / half) * (rows - half))) from there on (evaluated in double). */
+int zl_distance_bias_table(const float* table_host, int rows, int heads, double far, int n_dist, float* out_host);
 /* y[t][h] = o[t][h] / sqrt(mean(o[t][h]^2 over vdim) + eps) * weight[h * vdim + c] * sigmoid(gate[t * ldg + h * vdim + c]);
  * weight and gate may be NULL. */
 int zl_head_rmsnorm_gate(const float* o, long long ldo, const float* weight, const float* gate, long long ldg, void* y,
                          long long ldy, int T, int heads, int vdim, float eps, int out_dtype, int pdl, zl_stream_t stream);
+/* The same with the weight's stride between heads given (0: one weight of vdim shared by the heads) and the gate's
+ * function chosen: sigmoid(g) or silu(g) = g sigmoid(g). */
+enum { ZL_GATE_SIGMOID = 0, ZL_GATE_SILU = 1 };
+int zl_head_rmsnorm_gate_fn(const float* o, long long ldo, const float* weight, int weight_head_stride, const float* gate,
+                            long long ldg, int gate_fn, void* y, long long ldy, int T, int heads, int vdim, float eps,
+                            int out_dtype, int pdl, zl_stream_t stream);
+/* Queries and keys normed over the whole projection: from a projection row proj[t] (fp32), q = proj[q_off .. + heads * dim)
+ * divided by its RMS over all heads * dim entries, times q_weight (heads * dim) -> q_out (T, heads * dim) of `dtype`; the
+ * same for k = proj[k_off .. + kv_heads * dim) with k_weight -> row pos[t] of k_addrs[slot[t]]; the projected k itself
+ * (no norm) -> row pos[t] of v_addrs[slot[t]]: the values are the keys. */
+int zl_qk_fullnorm_append(const float* proj, long long ldp, int q_off, int k_off, int heads, int kv_heads, int dim,
+                          const float* q_weight, const float* k_weight, float eps, void* q_out, void* const* k_addrs,
+                          void* const* v_addrs, const int32_t* slot, const int32_t* pos, int T, int dtype, int pdl,
+                          zl_stream_t stream);
+/* Mixes of a token with its predecessor: out[s] (T, D) of out_dtype at out + s * out_stride elements,
+ * out[s][t] = x[t] + (prev - x[t]) * mu[s], mu fp32 (n_mix, D); prev = x[t - 1] when row t - 1 is of the same slot,
+ * zeros at position 0, else state_addrs[slot[t]] ((D) fp32, the slot's last token).  store_state != 0 (only when no two
+ * rows share a slot): x[t] also becomes the slot's last token; otherwise call zl_store_run_tails(x, ...) afterwards. */
+int zl_token_shift_mix(const float* x, long long ldx, const float* mu, int n_mix, void* const* state_addrs,
+                       const int32_t* slot, const int32_t* pos, void* out, long long out_stride, int T, int D,
+                       int store_state, int out_dtype, int pdl, zl_stream_t stream);
+/* Norm after the sum: x[t] <- weight * s / sqrt(mean(s^2) + eps), s = alpha x[t] + coef_a a[t] + coef_b b[t] (b NULL: no
+ * third term); x fp32; x_act != NULL also receives the new x[t] rounded to act_dtype. */
+int zl_postnorm_combine(float* x, long long ldx, float alpha, const float* a, long long lda, float coef_a, const float* b,
+                        long long ldb, float coef_b, const float* weight, void* x_act, int act_dtype, int T, int D, float eps,
+                        int pdl, zl_stream_t stream);
 /* x[t] += weight * s / sqrt(mean(s^2) + eps), s = sum_p coef[t * n_parts + p] * parts[(t * n_parts + p) * ldp ..] (coef
  * NULL: ones); x fp32.  x_act != NULL also receives the new x[t] rounded to act_dtype (the next Linear's input). */
 int zl_rmsnorm_residual_combine(const float* parts, long long ldp, const float* coef, int n_parts, const float* weight,
@@ -564,6 +613,32 @@ int zl_delta_rule(const float* r, long long ld_r, const float* k, long long ld_k
                   float unit_eps, const int32_t* run_row0, const int32_t* run_len, int runs, const int32_t* slot,
                   const int32_t* pos, void* const* state_addrs, float* o, long long ld_o, int heads, int dim_k, int dim_v,
                   int T, void* workspace, size_t workspace_bytes, int pdl, zl_stream_t stream);
+/* The last n_tail rows of every run of src (T, ld) fp32, columns col .. col + channels, into per-slot rings
+ * ring_addrs[slot] ((n_tail, channels) fp32): the row at position p goes to entry p % n_tail. */
+int zl_store_run_tails(const float* src, long long ld, int col, int channels, int n_tail, const int32_t* run_row0,
+                       const int32_t* run_len, int runs, const int32_t* slot, const int32_t* pos, void* const* ring_addrs,
+                       int pdl, zl_stream_t stream);
+/* Gated delta rule over the runs of a step, per head a (dim_k, dim_v) fp32 state in state_addrs[slot] (zero at position
+ * 0):  S <- g S;  e = beta (v - S^T k);  S <- S + k e^T;  o = S^T q.  proj (T, ld) fp32 holds, from column col_qkv, the
+ * projections q | k (kv_heads * dim_k each; head h uses q / k head h / (heads / kv_heads)) | v (heads * dim_v), at col_rate
+ * the logits of beta = sigmoid(.) (heads) and at col_decay the inputs of g = exp(-exp(a_log[h]) softplus(. + dt_bias[h])).
+ * q | k | v first pass a causal convolution per channel (conv_weight fp32 (channels, taps), last tap = the current token,
+ * zeros before position 0; the last taps - 1 inputs of a sequence live in ring_addrs[slot] ((taps - 1, channels) fp32, position
+ * p in entry p % (taps - 1)) and are updated by this call) and silu; then q, k <- x / sqrt(sum(x^2) + unit_eps) per head
+ * and q times q_scale.  Workspace of zl_delta_rule_workspace_bytes. */
+int zl_gated_delta_rule(const float* proj, long long ld, int col_qkv, int col_rate, int col_decay, const float* conv_weight,
+                        int taps, const float* a_log, const float* dt_bias, float unit_eps, float q_scale,
+                        void* const* ring_addrs, const int32_t* run_row0, const int32_t* run_len, int runs, const int32_t* slot,
+                        const int32_t* pos, void* const* state_addrs, float* o, long long ld_o, int heads, int kv_heads,
+                        int dim_k, int dim_v, int T, void* workspace, size_t workspace_bytes, int pdl, zl_stream_t stream);
+/* Decaying state with a bonus for the current token, same state layout:  o_t = (S + diag(bonus[h]) k_t v_t^T)^T r_t, then
+ * S <- diag(w_t) S + k_t v_t^T with w_t = exp(-exp(decay_logit_t)) per head and key channel.  Inputs fp32 (T, heads * dim),
+ * bonus fp32 (heads, dim_k).  Workspace of zl_delta_rule_workspace_bytes. */
+int zl_bonus_decay_scan(const float* r, long long ld_r, const float* k, long long ld_k, const float* v, long long ld_v,
+                        const float* decay_logit, long long ld_w, const float* bonus, const int32_t* run_row0,
+                        const int32_t* run_len, int runs, const int32_t* slot, const int32_t* pos, void* const* state_addrs,
+                        float* o, long long ld_o, int heads, int dim_k, int dim_v, int T, void* workspace,
+                        size_t workspace_bytes, int pdl, zl_stream_t stream);
 /* Routing of a mixture of experts: logits W_router x[t] (fp32), scores (sigmoid, or softmax over the experts), the
  * `top` largest of score + correction (NULL: none), weights = their scores (renormalize: divided by their sum) ->
  * top_experts / top_weights (T, top); and the (token, choice) pairs sorted by expert for zl_gemm_nt_grouped:
@@ -618,6 +693,52 @@ int zl_kodupel_read_layers(zl_kodupel_t* m, float* out_host, int T);
 int zl_kodupel_stats(zl_kodupel_t* m, double* weight_bytes, int* kernels_per_step);
 /* Copies one slot's recurrent state of layer `layer` ((heads, dim, dim) fp32) to the host (tests). */
 int zl_kodupel_read_state(zl_kodupel_t* m, int layer, int slot, float* out_host);
+
+/* ------------------------------------------------------------------------------------------ *
+ * Lagelorn: decoder-only model with learned positions and norm after the sum, x <- norm(alpha x + sublayer(x)) on an
+ * fp32 residual stream, whose layers are listed one by one.  A "delta" layer's mixer is a gated delta rule behind
+ * short convolutions; a "parallel" layer's mixer is the weighted sum of two mixers that read the same input: attention
+ * within blocks of positions (queries and keys normed over the whole projection, values = the projected keys, a
+ * learned bias by bucketed distance, a learned sink per head) and a decaying per-head state with a bonus for the
+ * current token whose inputs are mixes of the token with its predecessor.  The feed-forward, where a layer has one,
+ * is W_down (gelu_tanh(W_gate x) * (W_up x)) with biases.  After every layer a per-layer token embedding enters through
+ * a small gated projection and a norm.  The logits are soft-capped.  Same driver shape as zl_kodupel_*.
+ * ------------------------------------------------------------------------------------------ */
+enum { ZL_LAYER_DELTA = 0, ZL_LAYER_PARALLEL = 1 };
+typedef struct zl_lagelorn zl_lagelorn_t;
+typedef struct zl_lagelorn_layer {
+    int type;                              /* ZL_LAYER_* */
+    int heads, kv_heads, dim, vdim, conv;  /* delta: value heads, q / k heads, key size, value size, convolution taps */
+    int l_heads, l_kv_heads, l_dim;        /* parallel, attention: query heads, key heads, head size (values = keys) */
+    int l_chunk, l_rel_rows;               /* block of positions a token sees (0: all), rows of the distance table */
+    float l_bias_max, l_scale;             /* distance of the table's last logarithmic step, scale of q . k */
+    int r_heads, r_dim, r_decay_rank;      /* parallel, decaying state: heads, head size, inner size of the decay path */
+    float left_scale, right_scale;
+    int ff;                                /* feed-forward inner size, 0: none */
+} zl_lagelorn_layer_t;
+typedef struct zl_lagelorn_config {
+    int num_layers, width, vocab, max_positions, side_dim;
+    float eps, postln_alpha, logit_softcap;
+    int dtype;                             /* ZL_BF16 or ZL_F32 */
+    int max_batch, max_seq, max_step_tokens, use_pdl, use_graph;
+} zl_lagelorn_config_t;
+int zl_lagelorn_create(const zl_lagelorn_config_t* cfg, const zl_lagelorn_layer_t* layers, zl_lagelorn_t** out);
+void zl_lagelorn_destroy(zl_lagelorn_t* m);
+int zl_lagelorn_load_tensor(zl_lagelorn_t* m, const char* name, const void* data_host, int rows, int cols, int elem_bytes);
+int zl_lagelorn_init_synthetic(zl_lagelorn_t* m, uint64_t seed);
+int zl_lagelorn_finalize(zl_lagelorn_t* m);
+/* Same contract as zl_dekipel_step. */
+int zl_lagelorn_step(zl_lagelorn_t* m, const int32_t* tokens_host, const int32_t* slots_host, const int32_t* positions_host,
+                     int T, const int32_t* want_rows_host, int n_want, float* logits_host, int32_t* next_host);
+int zl_lagelorn_set_state(zl_lagelorn_t* m, const int32_t* tokens_host, const int32_t* positions_host, int B);
+int zl_lagelorn_step_device(zl_lagelorn_t* m, int B);
+int zl_lagelorn_sync(zl_lagelorn_t* m);
+zl_stream_t zl_lagelorn_stream(zl_lagelorn_t* m);
+int zl_lagelorn_capture_layers(zl_lagelorn_t* m, int on);
+int zl_lagelorn_read_layers(zl_lagelorn_t* m, float* out_host, int T);
+int zl_lagelorn_stats(zl_lagelorn_t* m, double* weight_bytes, int* kernels_per_step);
+/* Copies one slot's recurrent state of layer `layer` ((heads, dim_k, dim_v) fp32) to the host (tests). */
+int zl_lagelorn_read_state(zl_lagelorn_t* m, int layer, int slot, float* out_host);
 
 #ifdef __cplusplus
 }

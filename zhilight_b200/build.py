@@ -34,6 +34,7 @@ _FP32_RESIDUAL_COMMON = ["misc", "dense_gemm", "gemm_tiled", "group_norm_conv"]
 FAMILY_SOURCES = {
     "kodupel": _FP32_RESIDUAL_COMMON + ["mixer_rows", "moe_route", "delta_rule", "sink_attn", "kodupel_runner"],
     "dekipel": _FP32_RESIDUAL_COMMON + ["latent_attn", "dekipel_runner"],
+    "lagelorn": _FP32_RESIDUAL_COMMON + ["mixer_rows", "delta_rule", "sink_attn", "lagelorn_runner"],
 }
 
 

@@ -11,6 +11,16 @@
 // memory ahead of use.  The column lives in registers when dk is one of the compiled sizes, in shared memory otherwise.
 // A run that starts at position 0 starts from a zero state (a slot given to a new sequence needs no clearing); the
 // final state goes back to the slot.  Everything is fp32.
+//
+// Two more recurrences run on the same column kernel, each with a preparation kernel of its own that writes the same
+// six token vectors:
+//   * gated delta rule:  S <- g S;  e = beta (v - S^T k);  S <- S + k e^T;  o = S^T q, with a scalar decay g and a
+//     scalar rate beta per head and unit q, k.  Expanded, S_t = g S_(t-1) - (g beta k)(k^T S_(t-1)) + (beta k) v^T: the
+//     general form with u = k, a*u = g beta k, w = g in every channel and beta k as the written key.  Its q, k, v first
+//     pass a short causal convolution per channel (the last taps - 1 inputs of a sequence are kept per slot) and silu.
+//   * decay with a bonus for the current token:  o_t = (S_(t-1) + diag(b) k_t v_t^T)^T r_t;  S_t = diag(w_t) S_(t-1) + k_t v_t^T.
+//     The read-out comes before the write: o_t[j] = r_t . S_(t-1)[:, j] + (sum_i r_i b_i k_i) v_t[j], so the column
+//     kernel's dot product runs over r and the scalar in front of v_t[j] is prepared per (token, head) (READ_FIRST).
 #include "common.cuh"
 
 #include <cstdlib>
@@ -70,7 +80,7 @@ __device__ __forceinline__ void dr_cp_wait_all() { asm volatile("cp.async.wait_g
 // grid (dv / cols rounded up, H, runs); block = cols rounded up to a warp.  DK > 0: the column in registers.
 // The prepared vectors of the next chunk of tokens fly into the other half of the shared buffer (cp.async) while the
 // threads update their columns for the current chunk, so that no load sits on the chain from token to token.
-template <int DK>
+template <int DK, bool READ_FIRST>
 __global__ void k_delta_rule(DeltaP p) {
     extern __shared__ __align__(16) float dsm[];
     const int dk = DK > 0 ? DK : p.dk;
@@ -131,6 +141,18 @@ __global__ void k_delta_rule(DeltaP p) {
                 }
                 const float dot = (d0 + d1) + (d2 + d3);
                 float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+                if constexpr (READ_FIRST) {
+#pragma unroll
+                    for (int i = 0; i < DK; i += 4) {
+                        const float4 w = *reinterpret_cast<const float4*>(tv + 2 * DK + i);
+                        const float4 kk = *reinterpret_cast<const float4*>(tv + 3 * DK + i);
+                        S[i] = fmaf(kk.x, vj, w.x * S[i]);
+                        S[i + 1] = fmaf(kk.y, vj, w.y * S[i + 1]);
+                        S[i + 2] = fmaf(kk.z, vj, w.z * S[i + 2]);
+                        S[i + 3] = fmaf(kk.w, vj, w.w * S[i + 3]);
+                    }
+                    out = fmaf(tv[4 * DK], vj, dot);
+                } else {
 #pragma unroll
                 for (int i = 0; i < DK; i += 4) {
                     const float4 au = *reinterpret_cast<const float4*>(tv + DK + i);
@@ -144,13 +166,20 @@ __global__ void k_delta_rule(DeltaP p) {
                     o0 = fmaf(S[i], rr.x, o0), o1 = fmaf(S[i + 1], rr.y, o1), o2 = fmaf(S[i + 2], rr.z, o2), o3 = fmaf(S[i + 3], rr.w, o3);
                 }
                 out = (o0 + o1) + (o2 + o3);
+                }
             } else {
                 float dot = 0.f;
                 for (int i = 0; i < dk; ++i) dot = fmaf(tv[i], scol[(size_t)i * nth + tid], dot);
-                for (int i = 0; i < dk; ++i) {
-                    const float s = fmaf(tv[3 * dk + i], vj, fmaf(-tv[dk + i], dot, tv[2 * dk + i] * scol[(size_t)i * nth + tid]));
-                    scol[(size_t)i * nth + tid] = s;
-                    out = fmaf(s, tv[4 * dk + i], out);
+                if constexpr (READ_FIRST) {
+                    for (int i = 0; i < dk; ++i)
+                        scol[(size_t)i * nth + tid] = fmaf(tv[3 * dk + i], vj, tv[2 * dk + i] * scol[(size_t)i * nth + tid]);
+                    out = fmaf(tv[4 * dk], vj, dot);
+                } else {
+                    for (int i = 0; i < dk; ++i) {
+                        const float s = fmaf(tv[3 * dk + i], vj, fmaf(-tv[dk + i], dot, tv[2 * dk + i] * scol[(size_t)i * nth + tid]));
+                        scol[(size_t)i * nth + tid] = s;
+                        out = fmaf(s, tv[4 * dk + i], out);
+                    }
                 }
             }
             p.o[t * p.ld_o + (size_t)h * p.dv + j] = out;
@@ -178,18 +207,153 @@ static size_t delta_smem(int DK, int dk, int dv, int block) {
     return smem;
 }
 
-template <int DK>
+template <int DK, bool READ_FIRST>
 static int launch_delta(const DeltaP& p, int runs, int block, bool pdl, cudaStream_t st) {
     const size_t smem = delta_smem(DK, p.dk, p.dv, block);
     if (smem > 48 * 1024) {
         static size_t set_for = 0;
         if (smem > set_for) {
-            ZL_CHECK_CUDA(cudaFuncSetAttribute(k_delta_rule<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            ZL_CHECK_CUDA(cudaFuncSetAttribute(k_delta_rule<DK, READ_FIRST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             set_for = smem;
         }
     }
-    ZL_CHECK_CUDA(launch(k_delta_rule<DK>, dim3(cdiv(p.dv, p.cols), p.H, runs), dim3(block), smem, st, pdl, p));
+    ZL_CHECK_CUDA(launch(k_delta_rule<DK, READ_FIRST>, dim3(cdiv(p.dv, p.cols), p.H, runs), dim3(block), smem, st, pdl, p));
     return ZL_OK;
+}
+
+// the column kernel over prepared token vectors: registers for the compiled key sizes, shared memory otherwise
+template <bool READ_FIRST>
+static int run_columns(DeltaP& p, int runs, bool pdl, cudaStream_t st) {
+    // a warp of columns per CTA spreads one sequence over heads * dv / 32 CTAs
+    p.cols = 32;
+    const int block = 32;
+    static const bool no_reg_env = getenv("ZL_DELTA_NO_REG") != nullptr;
+    const bool no_reg = no_reg_env || (5 * p.dk + p.dv) % 4 != 0;   // the register kernel reads the staged vectors 16 bytes at a time
+    if (!no_reg && p.dk == 32) return launch_delta<32, READ_FIRST>(p, runs, block, pdl, st);
+    if (!no_reg && p.dk == 64) return launch_delta<64, READ_FIRST>(p, runs, block, pdl, st);
+    if (!no_reg && p.dk == 128) return launch_delta<128, READ_FIRST>(p, runs, block, pdl, st);
+    if (zl_delta_rule_prepare(p.dk, p.dv) != ZL_OK) return ZL_ERR_UNSUPPORTED;
+    return launch_delta<0, READ_FIRST>(p, runs, block, pdl, st);
+}
+
+// ---- gated delta rule with short convolutions --------------------------------------------------------------------------
+struct GatedPrepP {
+    const float* proj;          // (T, ld): q | k | v at col_qkv (G*dk, G*dk, H*dv channels), rate logits (H) at col_b, decay inputs (H) at col_a
+    long long ld;
+    int col_qkv, col_b, col_a;
+    int H, G, dk, dv, taps;
+    const float* conv_w;        // (C, taps), C = 2 G dk + H dv, the last tap is the current token's
+    const float *a_log, *dt_bias;   // (H)
+    void* const* ring_addrs;    // slot -> (taps - 1, C) fp32: input at position p sits in entry p % (taps - 1)
+    const int32_t *slot, *pos;
+    float unit_eps, q_scale;
+    int store_ring;             // every row is a run of its own: the kernel also stores its input into the ring
+    float* prep;
+};
+
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+// one CTA per token: convolution + silu of every channel into shared memory, then a warp per head writes the token vectors
+__global__ void __launch_bounds__(256) k_gated_delta_prep(GatedPrepP p) {
+    extern __shared__ float gsm[];   // C
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int C = 2 * p.G * p.dk + p.H * p.dv, nr = p.taps - 1;
+    const int sl = p.slot[t], pos = p.pos[t];
+    const float* row = p.proj + (size_t)t * p.ld + p.col_qkv;
+    float* ring = nr > 0 ? static_cast<float*>(p.ring_addrs[sl]) : nullptr;
+    // how many earlier rows of this step belong to the same sequence (at most taps - 1 matter)
+    int back = 0;
+    while (back < nr && t - back - 1 >= 0 && p.slot[t - back - 1] == sl) ++back;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const float* w = p.conv_w + (size_t)c * p.taps;
+        const float cur = row[c];
+        float acc = w[nr] * cur;
+        for (int j = 1; j <= nr; ++j) {   // the input j positions back
+            const int pj = pos - j;
+            if (pj < 0) break;
+            const float xin = j <= back ? row[c - (long long)j * p.ld] : ring[(size_t)(pj % nr) * C + c];
+            acc = fmaf(w[nr - j], xin, acc);
+        }
+        if (p.store_ring && nr > 0) ring[(size_t)(pos % nr) * C + c] = cur;
+        gsm[c] = silu_f(acc);
+    }
+    __syncthreads();
+    const int dk = p.dk, rep = p.H / p.G;
+    for (int h = warp; h < p.H; h += (int)(blockDim.x >> 5)) {
+        const int g = h / rep;
+        const float* q = gsm + (size_t)g * dk;
+        const float* k = gsm + (size_t)(p.G + g) * dk;
+        const float* v = gsm + (size_t)2 * p.G * dk + (size_t)h * p.dv;
+        float sq = 0.f, sk = 0.f;
+        for (int i = lane; i < dk; i += 32) sq = fmaf(q[i], q[i], sq), sk = fmaf(k[i], k[i], sk);
+        const float iq = p.q_scale / sqrtf(warp_sum(sq) + p.unit_eps), ik = 1.0f / sqrtf(warp_sum(sk) + p.unit_eps);
+        const float* prow = p.proj + (size_t)t * p.ld;
+        const float beta = 1.0f / (1.0f + expf(-prow[p.col_b + h]));
+        const float decay = expf(-expf(p.a_log[h]) * softplus_f(prow[p.col_a + h] + p.dt_bias[h]));
+        float* tv = p.prep + ((size_t)t * p.H + h) * (5 * dk + p.dv);
+        for (int i = lane; i < dk; i += 32) {
+            const float u = k[i] * ik;
+            tv[i] = u;
+            tv[dk + i] = decay * beta * u;
+            tv[2 * dk + i] = decay;
+            tv[3 * dk + i] = beta * u;
+            tv[4 * dk + i] = q[i] * iq;
+        }
+        for (int j = lane; j < p.dv; j += 32) tv[5 * dk + j] = v[j];
+    }
+}
+
+// The last n_tail rows of every run of a (T, ld) fp32 matrix, columns col .. col + C, into the slots' rings
+// (slot -> (n_tail, C)): the row at position p goes to entry p % n_tail.  grid (runs, n_tail)
+__global__ void __launch_bounds__(256) k_store_run_tails(const float* __restrict__ src, long long ld, int col, int C, int n_tail,
+                                                         const int32_t* __restrict__ run_row0, const int32_t* __restrict__ run_len,
+                                                         const int32_t* __restrict__ slot, const int32_t* __restrict__ pos,
+                                                         void* const* ring_addrs) {
+    pdl_trigger();
+    pdl_wait();
+    const int run = blockIdx.x, j = blockIdx.y, len = run_len[run];
+    if (j >= len) return;
+    const int row = run_row0[run] + len - 1 - j;
+    float* dst = static_cast<float*>(ring_addrs[slot[row]]) + (size_t)(pos[row] % n_tail) * C;
+    const float* s = src + (size_t)row * ld + col;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) dst[c] = s[c];
+}
+
+// ---- decay with a bonus for the current token ---------------------------------------------------------------------------
+struct BonusPrepP {
+    const float *r, *k, *v, *decay_logit;   // (T, H * dk) / v (T, H * dv)
+    long long ld_r, ld_k, ld_v, ld_w;
+    const float* bonus;                     // (H, dk)
+    int H, dk, dv;
+    float* prep;
+};
+// one warp per (token, head).  grid (ceil(H / 4), T).  w = exp(-exp(decay_logit))
+__global__ void __launch_bounds__(128) k_bonus_decay_prep(BonusPrepP p) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.y, h = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (h >= p.H) return;
+    const int dk = p.dk;
+    const float* rr = p.r + (size_t)t * p.ld_r + (size_t)h * dk;
+    const float* kr = p.k + (size_t)t * p.ld_k + (size_t)h * dk;
+    const float* wr = p.decay_logit + (size_t)t * p.ld_w + (size_t)h * dk;
+    const float* bo = p.bonus + (size_t)h * dk;
+    float* tv = p.prep + ((size_t)t * p.H + h) * (5 * dk + p.dv);
+    float s = 0.f;
+    for (int i = lane; i < dk; i += 32) {
+        const float r = rr[i], k = kr[i];
+        s = fmaf(r * bo[i], k, s);
+        tv[i] = r;
+        tv[dk + i] = 0.f;
+        tv[2 * dk + i] = expf(-expf(wr[i]));
+        tv[3 * dk + i] = k;
+        if (i > 0) tv[4 * dk + i] = 0.f;
+    }
+    s = warp_sum(s);
+    if (lane == 0) tv[4 * dk] = s;
+    for (int j = lane; j < p.dv; j += 32) tv[5 * dk + j] = p.v[(size_t)t * p.ld_v + (size_t)h * p.dv + j];
 }
 
 }  // namespace zl
@@ -219,14 +383,60 @@ extern "C" int zl_delta_rule(const float* r, long long ld_r, const float* k, lon
     DeltaP p{r, k, v, rate_logit, decay_logit, ld_r, ld_k, ld_v, ld_a, ld_w, run_row0, run_len, slot, pos, state_addrs, o, ld_o,
              heads, dim_k, dim_v, 0, decay_scale, unit_eps, static_cast<float*>(workspace), delta_chunk(dim_k, dim_v)};
     ZL_CHECK_CUDA(launch(k_delta_prep, dim3(cdiv(heads, 4), T), dim3(128), 0, stream, pdl != 0, p));
-    // a warp of columns per CTA spreads one sequence over heads * dv / 32 CTAs
-    p.cols = 32;
-    const int block = 32;
-    static const bool no_reg_env = getenv("ZL_DELTA_NO_REG") != nullptr;
-    const bool no_reg = no_reg_env || (5 * dim_k + dim_v) % 4 != 0;   // the register kernel reads the staged vectors 16 bytes at a time
-    if (!no_reg && dim_k == 32) return launch_delta<32>(p, runs, block, pdl != 0, stream);
-    if (!no_reg && dim_k == 64) return launch_delta<64>(p, runs, block, pdl != 0, stream);
-    if (!no_reg && dim_k == 128) return launch_delta<128>(p, runs, block, pdl != 0, stream);
-    if (zl_delta_rule_prepare(dim_k, dim_v) != ZL_OK) return ZL_ERR_UNSUPPORTED;
-    return launch_delta<0>(p, runs, block, pdl != 0, stream);
+    return run_columns<false>(p, runs, pdl != 0, stream);
+}
+
+extern "C" int zl_store_run_tails(const float* src, long long ld, int col, int channels, int n_tail, const int32_t* run_row0,
+                                  const int32_t* run_len, int runs, const int32_t* slot, const int32_t* pos,
+                                  void* const* ring_addrs, int pdl, zl_stream_t stream) {
+    ZL_CHECK_ARG(src && run_row0 && run_len && slot && pos && ring_addrs && channels > 0 && n_tail > 0 && n_tail <= 65535);
+    ZL_CHECK_ARG(runs > 0 && col >= 0 && ld >= col + channels);
+    ZL_CHECK_CUDA(launch(k_store_run_tails, dim3(runs, n_tail), dim3(256), 0, stream, pdl != 0, src, ld, col, channels, n_tail,
+                         run_row0, run_len, slot, pos, ring_addrs));
+    return ZL_OK;
+}
+
+extern "C" int zl_gated_delta_rule(const float* proj, long long ld, int col_qkv, int col_rate, int col_decay,
+                                   const float* conv_weight, int taps, const float* a_log, const float* dt_bias, float unit_eps,
+                                   float q_scale, void* const* ring_addrs, const int32_t* run_row0, const int32_t* run_len,
+                                   int runs, const int32_t* slot, const int32_t* pos, void* const* state_addrs, float* o,
+                                   long long ld_o, int heads, int kv_heads, int dim_k, int dim_v, int T, void* workspace,
+                                   size_t workspace_bytes, int pdl, zl_stream_t stream) {
+    ZL_CHECK_ARG(proj && conv_weight && a_log && dt_bias && run_row0 && run_len && slot && pos && state_addrs && o);
+    ZL_CHECK_ARG(taps >= 1 && (taps == 1 || ring_addrs) && heads > 0 && kv_heads > 0 && heads % kv_heads == 0);
+    ZL_CHECK_ARG(runs > 0 && runs <= 65535 && heads <= 65535 && dim_k > 0 && dim_v > 0);
+    ZL_CHECK_ARG(T > 0 && T <= 65535 && workspace && workspace_bytes >= zl_delta_rule_workspace_bytes(T, heads, dim_k, dim_v));
+    const int C = 2 * kv_heads * dim_k + heads * dim_v;
+    ZL_CHECK_SUPPORTED((size_t)C * 4 <= 200 * 1024);
+    GatedPrepP g{proj, ld, col_qkv, col_rate, col_decay, heads, kv_heads, dim_k, dim_v, taps, conv_weight, a_log, dt_bias,
+                 ring_addrs, slot, pos, unit_eps, q_scale, runs == T ? 1 : 0, static_cast<float*>(workspace)};
+    const size_t smem = (size_t)C * 4;
+    if (smem > 48 * 1024) {
+        static size_t set_for = 0;
+        if (smem > set_for) {
+            ZL_CHECK_CUDA(cudaFuncSetAttribute(k_gated_delta_prep, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            set_for = smem;
+        }
+    }
+    ZL_CHECK_CUDA(launch(k_gated_delta_prep, dim3(T), dim3(256), smem, stream, pdl != 0, g));
+    if (runs != T && taps > 1)   // rows of a run read ring entries that its last rows overwrite: stored afterwards
+        if (int rc_ = (zl_store_run_tails(proj, ld, col_qkv, C, taps - 1, run_row0, run_len, runs, slot, pos, ring_addrs, pdl, stream))) return rc_;
+    DeltaP p{nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0, run_row0, run_len, slot, pos, state_addrs, o, ld_o,
+             heads, dim_k, dim_v, 0, 0.f, 0.f, static_cast<float*>(workspace), delta_chunk(dim_k, dim_v)};
+    return run_columns<false>(p, runs, pdl != 0, stream);
+}
+
+extern "C" int zl_bonus_decay_scan(const float* r, long long ld_r, const float* k, long long ld_k, const float* v, long long ld_v,
+                                   const float* decay_logit, long long ld_w, const float* bonus, const int32_t* run_row0,
+                                   const int32_t* run_len, int runs, const int32_t* slot, const int32_t* pos,
+                                   void* const* state_addrs, float* o, long long ld_o, int heads, int dim_k, int dim_v, int T,
+                                   void* workspace, size_t workspace_bytes, int pdl, zl_stream_t stream) {
+    ZL_CHECK_ARG(r && k && v && decay_logit && bonus && run_row0 && run_len && slot && pos && state_addrs && o);
+    ZL_CHECK_ARG(runs > 0 && runs <= 65535 && heads > 0 && heads <= 65535 && dim_k > 0 && dim_v > 0);
+    ZL_CHECK_ARG(T > 0 && T <= 65535 && workspace && workspace_bytes >= zl_delta_rule_workspace_bytes(T, heads, dim_k, dim_v));
+    BonusPrepP b{r, k, v, decay_logit, ld_r, ld_k, ld_v, ld_w, bonus, heads, dim_k, dim_v, static_cast<float*>(workspace)};
+    ZL_CHECK_CUDA(launch(k_bonus_decay_prep, dim3(cdiv(heads, 4), T), dim3(128), 0, stream, pdl != 0, b));
+    DeltaP p{nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0, run_row0, run_len, slot, pos, state_addrs, o, ld_o,
+             heads, dim_k, dim_v, 0, 0.f, 0.f, static_cast<float*>(workspace), delta_chunk(dim_k, dim_v)};
+    return run_columns<true>(p, runs, pdl != 0, stream);
 }

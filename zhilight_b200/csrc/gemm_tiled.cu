@@ -1,6 +1,7 @@
 // General tiled GEMM y[b](M,N) = epi(x[b](M,K) @ w[b](N,K)^T) for any M, N, K, with a batch of strided problems
-// (one per attention head) and small fused epilogues: a per-column bias, relu^2, tanh, a sigmoid gate, and the clamped
-// gated unit of expert feed-forwards (columns 2j / 2j+1 hold gate / up, output column j).  Grouped mode serves
+// (one per attention head) and small fused epilogues: a per-column bias, relu^2, tanh, a sigmoid gate, the tanh form of
+// gelu times a per-element multiplier, a tanh soft cap, and gated units over column pairs (columns 2j / 2j+1 hold
+// gate / up, output column j): the clamped unit of expert feed-forwards and gelu_tanh(gate) * up.  Grouped mode serves
 // mixtures of experts: problem b owns the rows grp_off[b] .. grp_off[b+1] of a list sorted by expert, input rows are
 // gathered and output rows scattered through index lists, so one launch covers every expert of a step whatever
 // the routing turned out to be (the counts stay on the device: the launch can sit in a CUDA graph).
@@ -30,7 +31,12 @@ struct GemmP {
     const int32_t* y_rows = nullptr;  // sorted index -> row of y (identity when null)
     int act_tanh = 0;                 // few-rows kernel without the gated unit: tanh of the (biased) sum
     float limit = 0.f, alpha = 1.f, beta = 0.f;   // gated unit: g = min(gate, limit), u = clamp(up, +-limit), g sigmoid(alpha g) (u + beta)
+                                      // soft cap: limit * tanh(v / limit)
+    int pair_gelu = 0;                // few-rows kernel with a gated unit: gelu_tanh(gate) * up instead of the clamped unit
 };
+
+__host__ __device__ constexpr bool epi_pairs(int epi) { return epi == ZL_GEMM_EPI_GLU_CLAMP || epi == ZL_GEMM_EPI_GEGLU_TANH; }
+
 
 // rows of problem b and the place of its first row in the sorted list
 __device__ __forceinline__ void gemm_rows_of(const GemmP& p, int b, int& rows, int& first) {
@@ -48,6 +54,12 @@ __device__ __forceinline__ float glu_clamp(float gate, float up, const GemmP& p)
 }
 
 template <int EPI>
+__device__ __forceinline__ float pair_unit(float gate, float up, const GemmP& p) {
+    if constexpr (EPI == ZL_GEMM_EPI_GEGLU_TANH) return gelu_f(gate) * up;
+    else return glu_clamp(gate, up, p);
+}
+
+template <int EPI>
 __device__ __forceinline__ float gemm_epilogue(float v, const GemmP& p, int b, int m, int n) {
     if constexpr (EPI == ZL_GEMM_EPI_RELU2) {
         const float r = fmaxf(v, 0.f);
@@ -57,6 +69,10 @@ __device__ __forceinline__ float gemm_epilogue(float v, const GemmP& p, int b, i
         return v * (1.0f / (1.0f + expf(-g)));
     } else if constexpr (EPI == ZL_GEMM_EPI_TANH) {
         return tanhf(v);
+    } else if constexpr (EPI == ZL_GEMM_EPI_GELU_TANH_MUL) {
+        return gelu_f(v) * p.gate[(size_t)b * p.gb + (size_t)m * p.ldg + n];
+    } else if constexpr (EPI == ZL_GEMM_EPI_SOFTCAP) {
+        return p.limit * tanhf(v / p.limit);
     } else {
         return v;
     }
@@ -199,8 +215,8 @@ __global__ void __launch_bounds__(128) k_gemm_mma(GemmP p, int vec_x, int vec_w)
                     if (n < p.N) v0 += bias[n];
                     if (n + 1 < p.N) v1 += bias[n + 1];
                 }
-                if constexpr (EPI == ZL_GEMM_EPI_GLU_CLAMP) {
-                    if (n + 1 < p.N) y[yr + (n >> 1)] = from_f32<TO>(glu_clamp(v0, v1, p));
+                if constexpr (epi_pairs(EPI)) {
+                    if (n + 1 < p.N) y[yr + (n >> 1)] = from_f32<TO>(pair_unit<EPI>(v0, v1, p));
                 } else {
                     if (n < p.N) y[yr + n] = from_f32<TO>(gemm_epilogue<EPI>(v0, p, b, m, n));
                     if (n + 1 < p.N) y[yr + n + 1] = from_f32<TO>(gemm_epilogue<EPI>(v1, p, b, m, n + 1));
@@ -276,6 +292,8 @@ static cudaError_t launch_small_m(const GemmP& p, int batch, int epi, bool pdl, 
     if (epi == ZL_GEMM_EPI_RELU2) return launch_small_m_mt<T, TO, ZL_GEMM_EPI_RELU2>(p, batch, pdl, st);
     if (epi == ZL_GEMM_EPI_SIGMOID_GATE) return launch_small_m_mt<T, TO, ZL_GEMM_EPI_SIGMOID_GATE>(p, batch, pdl, st);
     if (epi == ZL_GEMM_EPI_TANH) return launch_small_m_mt<T, TO, ZL_GEMM_EPI_TANH>(p, batch, pdl, st);
+    if (epi == ZL_GEMM_EPI_GELU_TANH_MUL) return launch_small_m_mt<T, TO, ZL_GEMM_EPI_GELU_TANH_MUL>(p, batch, pdl, st);
+    if (epi == ZL_GEMM_EPI_SOFTCAP) return launch_small_m_mt<T, TO, ZL_GEMM_EPI_SOFTCAP>(p, batch, pdl, st);
     return launch_small_m_mt<T, TO, ZL_GEMM_EPI_NONE>(p, batch, pdl, st);
 }
 
@@ -345,7 +363,9 @@ __global__ void __launch_bounds__(256) k_gemm_grouped_small(GemmP p) {
             for (int m = 0; m < 8; ++m) {
                 float v = warp_sum(acc[m]);
                 if (GLU) {
-                    v = glu_clamp(v, warp_sum(acc2[m]), p);
+                    float v2 = warp_sum(acc2[m]);
+                    if (p.bias) v += p.bias[(size_t)b * p.bb + 2 * n], v2 += p.bias[(size_t)b * p.bb + 2 * n + 1];
+                    v = p.pair_gelu ? gelu_f(v) * v2 : glu_clamp(v, v2, p);
                 } else {
                     if (p.bias) v += p.bias[(size_t)b * p.bb + n];
                     if (p.act_tanh) v = tanhf(v);
@@ -450,11 +470,11 @@ __global__ void __launch_bounds__(256) k_gemm_f32(GemmP p, int vec_x, int vec_w)
             const int n = n0 + tx * 4 + j;
             if (bias && n < p.N) acc[i][j] += bias[n];
         }
-        if constexpr (EPI == ZL_GEMM_EPI_GLU_CLAMP) {
+        if constexpr (epi_pairs(EPI)) {
 #pragma unroll
             for (int j = 0; j < 4; j += 2) {
                 const int n = n0 + tx * 4 + j;
-                if (n + 1 < p.N) y[yr + (n >> 1)] = glu_clamp(acc[i][j], acc[i][j + 1], p);
+                if (n + 1 < p.N) y[yr + (n >> 1)] = pair_unit<EPI>(acc[i][j], acc[i][j + 1], p);
             }
         } else {
 #pragma unroll
@@ -475,6 +495,12 @@ static cudaError_t launch_mma(const GemmP& p, int batch, int epi, bool vx, bool 
     if (epi == ZL_GEMM_EPI_TANH) return launch(k_gemm_mma<T, TO, ZL_GEMM_EPI_TANH>, grid, block, 0, st, pdl, p, (int)vx, (int)vw);
     if (epi == ZL_GEMM_EPI_GLU_CLAMP)
         return launch(k_gemm_mma<T, TO, ZL_GEMM_EPI_GLU_CLAMP>, grid, block, 0, st, pdl, p, (int)vx, (int)vw);
+    if (epi == ZL_GEMM_EPI_GEGLU_TANH)
+        return launch(k_gemm_mma<T, TO, ZL_GEMM_EPI_GEGLU_TANH>, grid, block, 0, st, pdl, p, (int)vx, (int)vw);
+    if (epi == ZL_GEMM_EPI_GELU_TANH_MUL)
+        return launch(k_gemm_mma<T, TO, ZL_GEMM_EPI_GELU_TANH_MUL>, grid, block, 0, st, pdl, p, (int)vx, (int)vw);
+    if (epi == ZL_GEMM_EPI_SOFTCAP)
+        return launch(k_gemm_mma<T, TO, ZL_GEMM_EPI_SOFTCAP>, grid, block, 0, st, pdl, p, (int)vx, (int)vw);
     return launch(k_gemm_mma<T, TO, ZL_GEMM_EPI_NONE>, grid, block, 0, st, pdl, p, (int)vx, (int)vw);
 }
 
@@ -500,13 +526,15 @@ static int grouped_small_max() {
 
 static int gemm_dispatch(GemmP p, int batch, int in_dtype, int out_dtype, int epilogue, int pdl, cudaStream_t stream) {
     const int M = p.M, N = p.N, K = p.K;
-    const bool grouped = p.grp_off != nullptr, pairs = epilogue == ZL_GEMM_EPI_GLU_CLAMP;
+    const bool grouped = p.grp_off != nullptr, pairs = epi_pairs(epilogue);
     ZL_CHECK_ARG(p.x && p.w && p.y && M > 0 && N > 0 && K > 0 && batch > 0 && batch <= 65535);
     ZL_CHECK_ARG(p.ldx >= K && p.ldw >= K && p.ldy >= (pairs ? N / 2 : N));
     ZL_CHECK_ARG(in_dtype == ZL_F16 || in_dtype == ZL_BF16 || in_dtype == ZL_F32);
     ZL_CHECK_ARG(out_dtype == in_dtype || out_dtype == ZL_F32);
-    ZL_CHECK_ARG(epilogue >= ZL_GEMM_EPI_NONE && epilogue <= ZL_GEMM_EPI_GLU_CLAMP);
-    ZL_CHECK_ARG(epilogue != ZL_GEMM_EPI_SIGMOID_GATE || (p.gate && p.ldg >= N && !grouped));
+    ZL_CHECK_ARG(epilogue >= ZL_GEMM_EPI_NONE && epilogue <= ZL_GEMM_EPI_SOFTCAP);
+    const bool gated = epilogue == ZL_GEMM_EPI_SIGMOID_GATE || epilogue == ZL_GEMM_EPI_GELU_TANH_MUL;
+    ZL_CHECK_ARG(!gated || (p.gate && p.ldg >= N && !grouped));
+    ZL_CHECK_ARG(epilogue != ZL_GEMM_EPI_SOFTCAP || p.limit > 0.f);
     ZL_CHECK_ARG(!pairs || N % 2 == 0);
     ZL_CHECK_ARG(grouped || (!p.x_rows && !p.y_rows));
     ZL_CHECK_ARG(cdiv(M, kGB) <= 65535 && cdiv(N, kSmCols) <= 2147483647);
@@ -524,6 +552,12 @@ static int gemm_dispatch(GemmP p, int batch, int in_dtype, int out_dtype, int ep
             e = launch(k_gemm_f32<ZL_GEMM_EPI_TANH>, grid, block, 0, stream, pdl != 0, p, (int)vx, (int)vw);
         else if (epilogue == ZL_GEMM_EPI_GLU_CLAMP)
             e = launch(k_gemm_f32<ZL_GEMM_EPI_GLU_CLAMP>, grid, block, 0, stream, pdl != 0, p, (int)vx, (int)vw);
+        else if (epilogue == ZL_GEMM_EPI_GEGLU_TANH)
+            e = launch(k_gemm_f32<ZL_GEMM_EPI_GEGLU_TANH>, grid, block, 0, stream, pdl != 0, p, (int)vx, (int)vw);
+        else if (epilogue == ZL_GEMM_EPI_GELU_TANH_MUL)
+            e = launch(k_gemm_f32<ZL_GEMM_EPI_GELU_TANH_MUL>, grid, block, 0, stream, pdl != 0, p, (int)vx, (int)vw);
+        else if (epilogue == ZL_GEMM_EPI_SOFTCAP)
+            e = launch(k_gemm_f32<ZL_GEMM_EPI_SOFTCAP>, grid, block, 0, stream, pdl != 0, p, (int)vx, (int)vw);
         else
             e = launch(k_gemm_f32<ZL_GEMM_EPI_NONE>, grid, block, 0, stream, pdl != 0, p, (int)vx, (int)vw);
     } else if (grouped && M <= grouped_small_max() && vx && vw && K % 8 == 0 && (size_t)8 * K * 2 <= 160 * 1024 &&
@@ -534,6 +568,15 @@ static int gemm_dispatch(GemmP p, int batch, int in_dtype, int out_dtype, int ep
         else
             e = out_dtype == ZL_F32 ? launch_grouped_small<__half, float>(p, batch, pairs, pdl != 0, stream)
                                     : launch_grouped_small<__half, __half>(p, batch, pairs, pdl != 0, stream);
+    } else if (!grouped && epilogue == ZL_GEMM_EPI_GEGLU_TANH && batch == 1 && M <= 8 && vx && vw && K % 8 == 0 &&
+               (size_t)8 * K * 2 <= 160 * 1024) {   // a dense gated feed-forward of a decode step: gate and up rows streamed together
+        p.pair_gelu = 1;
+        if (in_dtype == ZL_BF16)
+            e = out_dtype == ZL_F32 ? launch_grouped_small<__nv_bfloat16, float>(p, 1, true, pdl != 0, stream)
+                                    : launch_grouped_small<__nv_bfloat16, __nv_bfloat16>(p, 1, true, pdl != 0, stream);
+        else
+            e = out_dtype == ZL_F32 ? launch_grouped_small<__half, float>(p, 1, true, pdl != 0, stream)
+                                    : launch_grouped_small<__half, __half>(p, 1, true, pdl != 0, stream);
     } else if (!grouped && epilogue == ZL_GEMM_EPI_TANH && batch == 1 && M <= 8 && vx && vw && K % 8 == 0 &&
                (size_t)8 * K * 2 <= 160 * 1024) {   // a narrow tanh projection of a decode step: one column per warp, loads in flight
         p.act_tanh = 1;
@@ -565,9 +608,19 @@ extern "C" int zl_gemm_nt(const void* x, long long ldx, long long x_batch_stride
                           long long w_batch_stride, void* y, long long ldy, long long y_batch_stride, int M, int N, int K,
                           int batch, int in_dtype, int out_dtype, int epilogue, const float* gate, long long ldg,
                           long long gate_batch_stride, int pdl, zl_stream_t stream) {
-    ZL_CHECK_ARG(epilogue != ZL_GEMM_EPI_GLU_CLAMP);
+    ZL_CHECK_ARG(!epi_pairs(epilogue) && epilogue != ZL_GEMM_EPI_SOFTCAP);
     GemmP p{x, w, y, gate, ldx, x_batch_stride, ldw, w_batch_stride, ldy, y_batch_stride, ldg, gate_batch_stride, M, N, K};
     return gemm_dispatch(p, batch, in_dtype, out_dtype, epilogue, pdl, stream);
+}
+
+extern "C" int zl_gemm_nt_fused(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* y,
+                                long long ldy, int M, int N, int K, int in_dtype, int out_dtype, int epilogue,
+                                const float* mul, long long ld_mul, float limit, int pdl, zl_stream_t stream) {
+    GemmP p{x, w, y, mul, ldx, 0, ldw, 0, ldy, 0, ld_mul, 0, M, N, K};
+    p.bias = bias;
+    p.limit = limit;
+    ZL_CHECK_ARG(epilogue != ZL_GEMM_EPI_GLU_CLAMP);
+    return gemm_dispatch(p, 1, in_dtype, out_dtype, epilogue, pdl, stream);
 }
 
 extern "C" int zl_gemm_nt_bias(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* y,

@@ -6,7 +6,12 @@
 //     by `mscale` (the frequencies are a table, so any scaling rule is the caller's), and the append of keys and values
 //     to the slot's caches;
 //   * RMS norm per head of a mixer's output with a full-width weight and a sigmoid gate;
-//   * the weighted sum of several parts per token (the chosen experts' outputs), RMS norm, residual add.
+//   * the weighted sum of several parts per token (the chosen experts' outputs), RMS norm, residual add;
+//   * RMS norm of queries and keys over the whole projection (all heads at once, a weight of that size), the unnormed key
+//     projection kept as the value, and the append to the slot's caches;
+//   * the mixes of a token with its predecessor, x + (x_prev - x) * mu_s for several coefficient vectors mu_s at once (the
+//     predecessor is the previous row of the run or the slot's stored last token);
+//   * norm after the sum: x <- w * rms(alpha x + c_a a + c_b b).
 #include "common.cuh"
 
 #include <cmath>
@@ -82,12 +87,13 @@ __global__ void __launch_bounds__(128) k_qkv_headnorm_rope_append(QkvPrepP p) {
     for (int c = rot + lane; c < n; c += 32) dst[c] = from_f32<TO>(src[c] * r * (w ? w[c] : 1.0f));
 }
 
-// y[t][h*dv + c] = o / sqrt(mean_c(o^2) + eps) * w[h*dv + c] * sigmoid(gate[t][h*dv + c]); one warp per (token, head)
+// y[t][h*dv + c] = o / sqrt(mean_c(o^2) + eps) * w[h*w_stride + c] * f(gate[t][h*dv + c]); f = sigmoid, or silu (gate_silu);
+// one warp per (token, head)
 template <typename TO>
 __global__ void __launch_bounds__(128) k_head_rmsnorm_gate(const float* __restrict__ o, long long ldo,
                                                            const float* __restrict__ w, const float* __restrict__ gate,
                                                            long long ldg, TO* __restrict__ y, long long ldy, int H, int dv,
-                                                           float eps) {
+                                                           float eps, int w_stride, int gate_silu) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.y, h = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -98,8 +104,11 @@ __global__ void __launch_bounds__(128) k_head_rmsnorm_gate(const float* __restri
     const float r = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
     for (int c = lane; c < dv; c += 32) {
         float v = src[c] * r;
-        if (w) v *= w[(size_t)h * dv + c];
-        if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + (size_t)h * dv + c]));
+        if (w) v *= w[(size_t)h * w_stride + c];
+        if (gate) {
+            const float gl = gate[(size_t)t * ldg + (size_t)h * dv + c], sg = 1.0f / (1.0f + expf(-gl));
+            v *= gate_silu ? gl * sg : sg;
+        }
         y[(size_t)t * ldy + (size_t)h * dv + c] = from_f32<TO>(v);
     }
 }
@@ -173,9 +182,177 @@ __global__ void __launch_bounds__(256) k_rmsnorm_residual_combine(const float* _
     }
 }
 
+// one CTA per token: q <- rms(q over all H*d) * q_w -> q_out; k <- rms(k over all G*d) * k_w -> key cache row; the
+// projected k itself -> value cache row
+template <typename TO>
+__global__ void __launch_bounds__(256) k_qk_fullnorm_append(const float* __restrict__ proj, long long ldp, int q_off, int k_off,
+                                                            int nq, int nk, const float* __restrict__ q_w,
+                                                            const float* __restrict__ k_w, float eps, TO* __restrict__ q_out,
+                                                            void* const* k_addrs, void* const* v_addrs,
+                                                            const int32_t* __restrict__ slot, const int32_t* __restrict__ pos) {
+    __shared__ float red[2][8];
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const float* q = proj + (size_t)t * ldp + q_off;
+    const float* k = proj + (size_t)t * ldp + k_off;
+    float sq = 0.f, sk = 0.f;
+    for (int c = threadIdx.x; c < nq; c += blockDim.x) sq = fmaf(q[c], q[c], sq);
+    for (int c = threadIdx.x; c < nk; c += blockDim.x) sk = fmaf(k[c], k[c], sk);
+    sq = warp_sum(sq), sk = warp_sum(sk);
+    if ((threadIdx.x & 31) == 0) red[0][threadIdx.x >> 5] = sq, red[1][threadIdx.x >> 5] = sk;
+    __syncthreads();
+    float tq = 0.f, tk = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tq += red[0][i], tk += red[1][i];
+    const float rq = 1.0f / sqrtf(tq / (float)nq + eps), rk = 1.0f / sqrtf(tk / (float)nk + eps);
+    TO* kd = static_cast<TO*>(k_addrs[slot[t]]) + (size_t)pos[t] * nk;
+    TO* vd = static_cast<TO*>(v_addrs[slot[t]]) + (size_t)pos[t] * nk;
+    for (int c = threadIdx.x; c < nq; c += blockDim.x) q_out[(size_t)t * nq + c] = from_f32<TO>(q[c] * rq * q_w[c]);
+    for (int c = threadIdx.x; c < nk; c += blockDim.x) {
+        kd[c] = from_f32<TO>(k[c] * rk * k_w[c]);
+        vd[c] = from_f32<TO>(k[c]);
+    }
+}
+
+// one CTA per token: out[s][t] = x[t] + (prev - x[t]) * mu[s], s < n_mix; prev = x[t - 1] when that row belongs to the same
+// sequence, zeros at position 0, else the slot's stored last token.  store_state: every row is a run of its own, so the
+// kernel also stores x[t] as the slot's last token (otherwise the caller stores the runs' tails afterwards).
+template <typename TO>
+__global__ void __launch_bounds__(256) k_token_shift_mix(const float* __restrict__ x, long long ldx, const float* __restrict__ mu,
+                                                         int n_mix, void* const* state_addrs, const int32_t* __restrict__ slot,
+                                                         const int32_t* __restrict__ pos, TO* __restrict__ out, long long out_stride,
+                                                         int D, int store_state) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, sl = slot[t];
+    const bool in_step = t > 0 && slot[t - 1] == sl, first = pos[t] == 0;
+    float* st = static_cast<float*>(state_addrs[sl]);
+    const float* xr = x + (size_t)t * ldx;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        const float cur = xr[c];
+        const float prev = in_step ? xr[c - ldx] : (first ? 0.f : st[c]);
+        const float dx = prev - cur;
+        for (int s = 0; s < n_mix; ++s) out[(size_t)s * out_stride + (size_t)t * D + c] = from_f32<TO>(fmaf(dx, mu[(size_t)s * D + c], cur));
+        if (store_state) st[c] = cur;
+    }
+}
+
+// one CTA per token: x <- w * s / sqrt(mean(s^2) + eps), s = alpha x + ca a + cb b (b may be null); also x rounded to TO
+template <typename TO>
+__global__ void __launch_bounds__(256) k_postnorm_combine(float* __restrict__ x, long long ldx, float alpha,
+                                                          const float* __restrict__ a, long long lda, float ca,
+                                                          const float* __restrict__ b, long long ldb, float cb,
+                                                          const float* __restrict__ w, TO* __restrict__ x_act, int D, float eps) {
+    extern __shared__ float psm[];   // D
+    __shared__ float red[8];
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        float s = fmaf(ca, a[(size_t)t * lda + c], alpha * x[(size_t)t * ldx + c]);
+        if (b) s = fmaf(cb, b[(size_t)t * ldb + c], s);
+        psm[c] = s;
+        ss = fmaf(s, s, ss);
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
+    const float r = 1.0f / sqrtf(tot / (float)D + eps);
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        const float nx = psm[c] * r * w[c];
+        x[(size_t)t * ldx + c] = nx;
+        if (x_act) x_act[(size_t)t * D + c] = from_f32<TO>(nx);
+    }
+}
+
 }  // namespace zl
 
 using namespace zl;
+
+extern "C" int zl_qk_fullnorm_append(const float* proj, long long ldp, int q_off, int k_off, int heads, int kv_heads, int dim,
+                                     const float* q_weight, const float* k_weight, float eps, void* q_out, void* const* k_addrs,
+                                     void* const* v_addrs, const int32_t* slot, const int32_t* pos, int T, int dtype, int pdl,
+                                     zl_stream_t stream) {
+    ZL_CHECK_ARG(proj && q_weight && k_weight && q_out && k_addrs && v_addrs && slot && pos && T > 0);
+    ZL_CHECK_ARG(heads > 0 && kv_heads > 0 && dim > 0 && q_off >= 0 && k_off >= 0);
+    ZL_CHECK_ARG(dtype == ZL_F16 || dtype == ZL_BF16 || dtype == ZL_F32);
+    const int nq = heads * dim, nk = kv_heads * dim;
+    cudaError_t e;
+    if (dtype == ZL_F32)
+        e = launch(k_qk_fullnorm_append<float>, dim3(T), dim3(256), 0, stream, pdl != 0, proj, ldp, q_off, k_off, nq, nk, q_weight,
+                   k_weight, eps, (float*)q_out, k_addrs, v_addrs, slot, pos);
+    else if (dtype == ZL_BF16)
+        e = launch(k_qk_fullnorm_append<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, pdl != 0, proj, ldp, q_off, k_off, nq, nk,
+                   q_weight, k_weight, eps, (__nv_bfloat16*)q_out, k_addrs, v_addrs, slot, pos);
+    else
+        e = launch(k_qk_fullnorm_append<__half>, dim3(T), dim3(256), 0, stream, pdl != 0, proj, ldp, q_off, k_off, nq, nk, q_weight,
+                   k_weight, eps, (__half*)q_out, k_addrs, v_addrs, slot, pos);
+    ZL_CHECK_CUDA(e);
+    return ZL_OK;
+}
+
+extern "C" int zl_token_shift_mix(const float* x, long long ldx, const float* mu, int n_mix, void* const* state_addrs,
+                                  const int32_t* slot, const int32_t* pos, void* out, long long out_stride, int T, int D,
+                                  int store_state, int out_dtype, int pdl, zl_stream_t stream) {
+    ZL_CHECK_ARG(x && mu && state_addrs && slot && pos && out && n_mix > 0 && T > 0 && D > 0 && ldx >= D);
+    ZL_CHECK_ARG(out_stride >= (long long)T * D);
+    ZL_CHECK_ARG(out_dtype == ZL_F16 || out_dtype == ZL_BF16 || out_dtype == ZL_F32);
+    cudaError_t e;
+    if (out_dtype == ZL_F32)
+        e = launch(k_token_shift_mix<float>, dim3(T), dim3(256), 0, stream, pdl != 0, x, ldx, mu, n_mix, state_addrs, slot, pos,
+                   (float*)out, out_stride, D, store_state);
+    else if (out_dtype == ZL_BF16)
+        e = launch(k_token_shift_mix<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, pdl != 0, x, ldx, mu, n_mix, state_addrs, slot,
+                   pos, (__nv_bfloat16*)out, out_stride, D, store_state);
+    else
+        e = launch(k_token_shift_mix<__half>, dim3(T), dim3(256), 0, stream, pdl != 0, x, ldx, mu, n_mix, state_addrs, slot, pos,
+                   (__half*)out, out_stride, D, store_state);
+    ZL_CHECK_CUDA(e);
+    return ZL_OK;
+}
+
+extern "C" int zl_postnorm_combine(float* x, long long ldx, float alpha, const float* a, long long lda, float coef_a,
+                                   const float* b, long long ldb, float coef_b, const float* weight, void* x_act, int act_dtype,
+                                   int T, int D, float eps, int pdl, zl_stream_t stream) {
+    ZL_CHECK_ARG(x && a && weight && T > 0 && D > 0 && ldx >= D && lda >= D && (!b || ldb >= D));
+    ZL_CHECK_ARG(!x_act || act_dtype == ZL_F16 || act_dtype == ZL_BF16);
+    ZL_CHECK_SUPPORTED((size_t)D * 4 <= 48 * 1024);
+    cudaError_t e;
+    const size_t smem = (size_t)D * 4;
+    if (x_act && act_dtype == ZL_F16)
+        e = launch(k_postnorm_combine<__half>, dim3(T), dim3(256), smem, stream, pdl != 0, x, ldx, alpha, a, lda, coef_a, b, ldb,
+                   coef_b, weight, (__half*)x_act, D, eps);
+    else
+        e = launch(k_postnorm_combine<__nv_bfloat16>, dim3(T), dim3(256), smem, stream, pdl != 0, x, ldx, alpha, a, lda, coef_a, b,
+                   ldb, coef_b, weight, (__nv_bfloat16*)x_act, D, eps);
+    ZL_CHECK_CUDA(e);
+    return ZL_OK;
+}
+
+extern "C" int zl_head_rmsnorm_gate_fn(const float* o, long long ldo, const float* weight, int weight_head_stride,
+                                       const float* gate, long long ldg, int gate_fn, void* y, long long ldy, int T, int heads,
+                                       int vdim, float eps, int out_dtype, int pdl, zl_stream_t stream) {
+    ZL_CHECK_ARG(o && y && T > 0 && heads > 0 && vdim > 0 && (gate_fn == ZL_GATE_SIGMOID || gate_fn == ZL_GATE_SILU));
+    ZL_CHECK_ARG(weight_head_stride == 0 || weight_head_stride >= vdim);
+    ZL_CHECK_ARG(out_dtype == ZL_F16 || out_dtype == ZL_BF16 || out_dtype == ZL_F32);
+    const dim3 grid(cdiv(heads, 4), T), block(128);
+    const int silu = gate_fn == ZL_GATE_SILU;
+    cudaError_t e;
+    if (out_dtype == ZL_F32)
+        e = launch(k_head_rmsnorm_gate<float>, grid, block, 0, stream, pdl != 0, o, ldo, weight, gate, ldg, (float*)y, ldy, heads,
+                   vdim, eps, weight_head_stride, silu);
+    else if (out_dtype == ZL_BF16)
+        e = launch(k_head_rmsnorm_gate<__nv_bfloat16>, grid, block, 0, stream, pdl != 0, o, ldo, weight, gate, ldg,
+                   (__nv_bfloat16*)y, ldy, heads, vdim, eps, weight_head_stride, silu);
+    else
+        e = launch(k_head_rmsnorm_gate<__half>, grid, block, 0, stream, pdl != 0, o, ldo, weight, gate, ldg, (__half*)y, ldy,
+                   heads, vdim, eps, weight_head_stride, silu);
+    ZL_CHECK_CUDA(e);
+    return ZL_OK;
+}
 
 extern "C" int zl_qkv_headnorm_rope_append(const float* proj, long long ldp, int q_off, int k_off, int v_off, int heads,
                                            int kv_heads, int dim, int vdim, const float* q_weight, const float* k_weight,
@@ -201,21 +378,8 @@ extern "C" int zl_qkv_headnorm_rope_append(const float* proj, long long ldp, int
 extern "C" int zl_head_rmsnorm_gate(const float* o, long long ldo, const float* weight, const float* gate, long long ldg,
                                     void* y, long long ldy, int T, int heads, int vdim, float eps, int out_dtype, int pdl,
                                     zl_stream_t stream) {
-    ZL_CHECK_ARG(o && y && T > 0 && heads > 0 && vdim > 0);
-    ZL_CHECK_ARG(out_dtype == ZL_F16 || out_dtype == ZL_BF16 || out_dtype == ZL_F32);
-    const dim3 grid(cdiv(heads, 4), T), block(128);
-    cudaError_t e;
-    if (out_dtype == ZL_F32)
-        e = launch(k_head_rmsnorm_gate<float>, grid, block, 0, stream, pdl != 0, o, ldo, weight, gate, ldg, (float*)y, ldy, heads,
-                   vdim, eps);
-    else if (out_dtype == ZL_BF16)
-        e = launch(k_head_rmsnorm_gate<__nv_bfloat16>, grid, block, 0, stream, pdl != 0, o, ldo, weight, gate, ldg,
-                   (__nv_bfloat16*)y, ldy, heads, vdim, eps);
-    else
-        e = launch(k_head_rmsnorm_gate<__half>, grid, block, 0, stream, pdl != 0, o, ldo, weight, gate, ldg, (__half*)y, ldy,
-                   heads, vdim, eps);
-    ZL_CHECK_CUDA(e);
-    return ZL_OK;
+    return zl_head_rmsnorm_gate_fn(o, ldo, weight, vdim, gate, ldg, ZL_GATE_SIGMOID, y, ldy, T, heads, vdim, eps, out_dtype, pdl,
+                                   stream);
 }
 
 extern "C" int zl_rmsnorm_residual_combine(const float* parts, long long ldp, const float* coef, int n_parts,

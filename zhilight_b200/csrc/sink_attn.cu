@@ -2,6 +2,9 @@
 // one extra term exp(sink) that has no value (sink = 0 adds exactly one), and an optional sigmoid gate per head on
 // the output.  Token t of the step sees rows 0 .. pos[t] of the caches of slot[t]; the step's own keys and values are
 // appended before this runs, so prompts, portions of prompts and single decode tokens are the same case.
+// Two optional restrictions of the general form: with chunk > 0 a token sees only the keys of its own block of `chunk`
+// positions (blocks counted from position 0 of the sequence), and with a distance table the score of (token, key)
+// gets dist_bias[h][min(pos - key, n_dist - 1)] added after the scale.
 //
 // k_sink_attn_mma (16-bit caches, head sizes that are multiples of 16, values up to 128 wide, at most 16 query heads per
 // key/value head): a CTA owns up to 64 rows = (consecutive tokens of one run) x (the query heads of one key/value
@@ -15,6 +18,7 @@
 // does not depend on the step it is computed in) with an online softmax each, merged in warp order with the sink term.
 #include "common.cuh"
 
+#include <cmath>
 #include <cstdlib>
 #include <type_traits>
 
@@ -35,7 +39,13 @@ struct SinkAttnP {
     float scale;
     int splits;
     float* ws;                 // splits > 1: (T, H, splits, 2 + vd) partial (max, sum, weighted values)
+    int chunk = 0;             // > 0: keys below (pos / chunk) * chunk are not seen
+    const float* dist_bias = nullptr;   // (H, n_dist) added to the scaled score by distance, or null
+    int n_dist = 0;
 };
+
+// first key a token at `pos` sees
+__device__ __forceinline__ int sa_first_key(const SinkAttnP& p, int pos) { return p.chunk > 0 ? (pos / p.chunk) * p.chunk : 0; }
 
 template <typename T>
 __global__ void __launch_bounds__(kSaWarps * 32) k_sink_attn(SinkAttnP p) {
@@ -58,17 +68,19 @@ __global__ void __launch_bounds__(kSaWarps * 32) k_sink_attn(SinkAttnP p) {
 #pragma unroll
     for (int i = 0; i < kSaMaxPerLane; ++i) acc[i] = 0.f;
     // keys of this split: a range of whole groups of kSaWarps keys
-    int j_lo = 0, j_hi = pos + 1;
+    int j_lo = sa_first_key(p, pos), j_hi = pos + 1;
     if (p.splits > 1) {
-        const int per = cdiv(cdiv(pos + 1, p.splits), kSaWarps) * kSaWarps;
-        j_lo = blockIdx.z * per;
+        const int per = cdiv(cdiv(pos + 1 - j_lo, p.splits), kSaWarps) * kSaWarps;
+        j_lo += blockIdx.z * per;
         j_hi = min(pos + 1, j_lo + per);
     }
+    const float* bias = p.dist_bias ? p.dist_bias + (size_t)h * p.n_dist : nullptr;
     for (int j = j_lo + warp; j < j_hi; j += kSaWarps) {
         const T* kr = kc + (size_t)j * kst;
         float s = 0.f;
         for (int c = lane; c < p.d; c += 32) s = fmaf(sq[c], to_f32<T>(kr[c]), s);
         s = warp_sum(s);
+        if (bias) s += bias[min(pos - j, p.n_dist - 1)];
         const float mn = fmaxf(m, s), corr = expf(m - mn), w = expf(s - mn);
         l = fmaf(l, corr, w);
         const T* vr = vc + (size_t)j * vst;
@@ -179,10 +191,11 @@ __global__ void __launch_bounds__(128) k_sink_attn_mma(SinkAttnMmaP pp) {
     const int ntok = min(nq, len - t0), row0 = pp.run_row0[run] + t0;
     const int sl = p.slot[row0], pos0 = p.pos[row0];
     const int n_keys = pos0 + ntok;
-    int k_lo = 0, k_hi = n_keys;
+    // key tiles start at multiples of kTk from key 0 whatever the step, so a token's sums do not depend on the cut
+    int k_lo = (sa_first_key(p, pos0) / kTk) * kTk, k_hi = n_keys;
     if (p.splits > 1) {
-        const int per = cdiv(cdiv(n_keys, p.splits), kTk) * kTk;
-        k_lo = split * per;
+        const int per = cdiv(cdiv(n_keys - k_lo, p.splits), kTk) * kTk;
+        k_lo += split * per;
         k_hi = min(n_keys, k_lo + per);
     }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
@@ -207,8 +220,9 @@ __global__ void __launch_bounds__(128) k_sink_attn_mma(SinkAttnMmaP pp) {
     };
     // rows of this thread: wrow + gq and + 8; row -> (token, head in the group).  kb: the warp's first key in a key tile
     const int wrow = DEC ? 0 : warp * 16, kb = DEC ? warp * 16 : 0;
-    int tok_of[2], pos_of[2], head_of[2];
+    int tok_of[2], pos_of[2], head_of[2], first_of[2];
     bool row_ok[2];
+    const float* bias_of[2];
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
         const int r = wrow + gq + hh * 8;
@@ -216,6 +230,8 @@ __global__ void __launch_bounds__(128) k_sink_attn_mma(SinkAttnMmaP pp) {
         head_of[hh] = g * R + (r - tok_of[hh] * R);
         row_ok[hh] = tok_of[hh] < ntok;
         pos_of[hh] = pos0 + tok_of[hh];
+        first_of[hh] = sa_first_key(p, pos_of[hh]);
+        bias_of[hh] = p.dist_bias ? p.dist_bias + (size_t)(head_of[hh] < p.H ? head_of[hh] : 0) * p.n_dist : nullptr;
     }
     float m_run[2], l_run[2], O[NV][4];
 #pragma unroll
@@ -271,8 +287,10 @@ __global__ void __launch_bounds__(128) k_sink_attn_mma(SinkAttnMmaP pp) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     const int hh = c >> 1, key = k0 + kb + 8 * j + 2 * tq + (c & 1);
-                    const bool ok = row_ok[hh] && key < k_hi && key <= pos_of[hh];
-                    S[j][c] = ok ? S[j][c] * p.scale : -1e30f;
+                    const bool ok = row_ok[hh] && key < k_hi && key <= pos_of[hh] && key >= first_of[hh];
+                    float sc = S[j][c] * p.scale;
+                    if (ok && bias_of[hh]) sc += bias_of[hh][min(pos_of[hh] - key, p.n_dist - 1)];
+                    S[j][c] = ok ? sc : -1e30f;
                     mx[hh] = fmaxf(mx[hh], S[j][c]);
                 }
             float corr[2];
@@ -497,6 +515,33 @@ extern "C" int zl_sink_attention(const void* q, void* const* k_addrs, void* cons
                                  int T, int heads, int kv_heads, int dim, int vdim, int splits, void* workspace,
                                  size_t workspace_bytes, const int32_t* run_row0, const int32_t* run_len, int runs,
                                  int max_run_len, int dtype, int pdl, zl_stream_t stream) {
+    return zl_sink_attention_local(q, k_addrs, v_addrs, slot, pos, sink, gate, ldg, scale, 0, nullptr, 0, out, T, heads, kv_heads,
+                                   dim, vdim, splits, workspace, workspace_bytes, run_row0, run_len, runs, max_run_len, dtype,
+                                   pdl, stream);
+}
+
+extern "C" int zl_distance_bias_table(const float* table_host, int rows, int heads, double far, int n_dist, float* out_host) {
+    ZL_CHECK_ARG(table_host && out_host && rows > 0 && heads > 0 && n_dist > 0);
+    const int half = rows / 2;
+    ZL_CHECK_ARG(rows == 1 || (half > 0 && far > (double)half));
+    for (int n = 0; n < n_dist; ++n) {
+        int b = n;
+        if (n >= half) {
+            b = rows == 1 ? 0 : half + (int)floor(log((double)n / half) / log(far / half) * (double)(rows - half));
+            if (b > rows - 1) b = rows - 1;
+        }
+        for (int h = 0; h < heads; ++h) out_host[(size_t)h * n_dist + n] = table_host[(size_t)b * heads + h];
+    }
+    return ZL_OK;
+}
+
+extern "C" int zl_sink_attention_local(const void* q, void* const* k_addrs, void* const* v_addrs, const int32_t* slot,
+                                       const int32_t* pos, const float* sink, const float* gate, long long ldg, float scale,
+                                       int chunk, const float* dist_bias, int n_dist, void* out, int T, int heads, int kv_heads,
+                                       int dim, int vdim, int splits, void* workspace, size_t workspace_bytes,
+                                       const int32_t* run_row0, const int32_t* run_len, int runs, int max_run_len, int dtype,
+                                       int pdl, zl_stream_t stream) {
+    ZL_CHECK_ARG(chunk >= 0 && (!dist_bias || n_dist > 0));
     ZL_CHECK_ARG(q && k_addrs && v_addrs && slot && pos && out && T > 0 && T <= 65535 && heads > 0 && kv_heads > 0);
     ZL_CHECK_ARG(heads % kv_heads == 0 && dim > 0 && vdim > 0);
     ZL_CHECK_SUPPORTED(vdim <= 32 * kSaMaxPerLane);
@@ -505,6 +550,9 @@ extern "C" int zl_sink_attention(const void* q, void* const* k_addrs, void* cons
     ZL_CHECK_ARG(splits == 1 || (workspace && workspace_bytes >= zl_sink_attention_workspace_bytes(T, heads, vdim, splits)));
     SinkAttnP p{q, k_addrs, v_addrs, slot, pos, sink, gate, ldg, out, heads, kv_heads, dim, vdim, scale, splits,
                 static_cast<float*>(workspace)};
+    p.chunk = chunk;
+    p.dist_bias = dist_bias;
+    p.n_dist = n_dist;
     const dim3 grid(heads, T, splits), block(kSaWarps * 32);
     const size_t smem = ((size_t)dim + 2 * kSaWarps + (size_t)kSaWarps * vdim) * sizeof(float);
     cudaError_t e;

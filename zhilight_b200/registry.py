@@ -84,6 +84,16 @@ def _build_kodupel(config, dtype, max_batch, max_seq, max_step_tokens, **kw):
 register("Kodupel", _build_kodupel, ("bfloat16", "float32"))
 
 
+# ---- Lagelorn --------------------------------------------------------------------------------------------------------
+def _build_lagelorn(config, dtype, max_batch, max_seq, max_step_tokens, **kw):
+    from .lagelorn import LagelornDecoder
+    return LagelornDecoder.from_config_dict(config, dtype=dtype, max_batch=max_batch, max_seq=max_seq,
+                                            max_step_tokens=max_step_tokens, **kw)
+
+
+register("Lagelorn", _build_lagelorn, ("bfloat16", "float32"))
+
+
 # ---- Llama (HF folder) -----------------------------------------------------------------------------------------------
 _HF_LLAMA_NAMES = [
     (r"^model\.embed_tokens\.weight$", "token_embedding.weight"),
