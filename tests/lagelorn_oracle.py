@@ -99,7 +99,7 @@ def bonus_decay_scan(r, k, v, w, u):
     return out, S
 
 
-def right_mixer(h, W, p, mc, eps):
+def right_mixer(h, W, p, mc, eps, keep=None):
     H, d = mc["heads"], mc["dim"]
     T = h.shape[0]
     dx = shifted(h) - h
@@ -109,7 +109,9 @@ def right_mixer(h, W, p, mc, eps):
     v = (mix["v"] @ W[p + "v"].T).reshape(T, H, d)
     gate = silu(mix["g"] @ W[p + "g"].T)
     w = np.exp(-np.exp(np.tanh(mix["w"] @ W[p + "w1"].T) @ W[p + "w2"].T + W[p + "w0"])).reshape(T, H, d)
-    o, _ = bonus_decay_scan(r, k, v, w, W[p + "u"])
+    o, S = bonus_decay_scan(r, k, v, w, W[p + "u"])
+    if keep is not None:
+        keep.append(S)
     o = o / np.sqrt(np.mean(o * o, axis=-1, keepdims=True) + eps)
     return (o.reshape(T, -1) * W[p + "norm"] * gate) @ W[p + "o"].T
 
@@ -141,7 +143,7 @@ def gated_delta_scan(q, k, v, beta, g):
     return out, S
 
 
-def delta_mixer(h, W, p, mc, eps):
+def delta_mixer(h, W, p, mc, eps, keep=None):
     H, G, d, dv = mc["heads"], mc["kv_heads"], mc["dim"], mc["vdim"]
     T = h.shape[0]
     rep = H // G
@@ -154,7 +156,9 @@ def delta_mixer(h, W, p, mc, eps):
     k = np.repeat(k, rep, axis=1)
     beta = sigmoid(h @ W[p + "b"].T)
     g = np.exp(-np.exp(W[p + "A_log"]) * softplus(h @ W[p + "a"].T + W[p + "dt_bias"]))
-    o, _ = gated_delta_scan(q, k, v, beta, g)
+    o, S = gated_delta_scan(q, k, v, beta, g)
+    if keep is not None:
+        keep.append(S)
     o = o / np.sqrt(np.mean(o * o, axis=-1, keepdims=True) + eps) * W[p + "norm"]
     return (o.reshape(T, -1) * silu(h @ W[p + "g"].T)) @ W[p + "o"].T
 
@@ -171,16 +175,16 @@ def side_input(x, tokens, W, i, dim, eps):
     return x + y / np.sqrt(np.mean(y * y, axis=-1, keepdims=True) + eps) * W[p + "norm"]
 
 
-def layer(x, tokens, W, cfg, i):
+def layer(x, tokens, W, cfg, i, keep=None):
     lc = cfg["layers"][i]
     eps, alpha = cfg["norm"]["eps"], cfg["postln_alpha"]
     p = "l%d." % i
     if lc["type"] == "delta":
-        m = delta_mixer(x, W, p + "mix.", lc["mixer"], eps)
+        m = delta_mixer(x, W, p + "mix.", lc["mixer"], eps, keep)
     else:
         mc = lc["mixer"]
         m = mc["left_scale"] * left_mixer(x, W, p + "mix.left.", mc["left"], eps) + \
-            mc["right_scale"] * right_mixer(x, W, p + "mix.right.", mc["right"], eps)
+            mc["right_scale"] * right_mixer(x, W, p + "mix.right.", mc["right"], eps, keep)
     x = rms_norm(alpha * x + m, W[p + "norm1"], eps)
     if lc.get("mlp") is not None:
         x = rms_norm(alpha * x + dense_ff(x, W, p + "mlp."), W[p + "norm2"], eps)
@@ -189,13 +193,55 @@ def layer(x, tokens, W, cfg, i):
 
 def model(tokens, W, cfg, return_layers=False):
     """Logits (T, vocab) of one sequence from position 0; with return_layers also the stream after every layer."""
+    z, streams, _ = forward(cfg, W, tokens)
+    return (z, streams) if return_layers else z
+
+
+def forward(cfg, W, tokens):
+    """-> (logits (T, vocab), the stream after every layer (L, T, width), the final recurrent state of every layer)."""
     tokens = np.asarray(tokens)
     x = W["embed"][tokens] + W["pos"][:len(tokens)]
-    streams = []
+    streams, states = [], []
     for i in range(len(cfg["layers"])):
-        x = layer(x, tokens, W, cfg, i)
+        x = layer(x, tokens, W, cfg, i, states)
         streams.append(x)
     z = rms_norm(x, W["final.norm"], cfg["norm"]["eps"]) @ W["head"].T
     cap = cfg["logit_softcap"]
-    z = cap * np.tanh(z / cap)
-    return (z, np.stack(streams)) if return_layers else z
+    return cap * np.tanh(z / cap), np.stack(streams), states
+
+
+def bf16_round(a):
+    """float32 array rounded to the nearest bfloat16 (ties to even), still float32."""
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+    return u.astype(np.uint32).view(np.float32).reshape(np.shape(a))
+
+
+def random_weights(shapes, seed=0):
+    """shapes: name -> shape.  -> name -> float32 array whose values are exact in bfloat16."""
+    rng = np.random.default_rng(seed)
+    W = {}
+    for name, shp in sorted(shapes.items()):
+        last = name.rsplit(".", 1)[-1]
+        if last in ("norm", "norm1", "norm2") and "side" not in name:
+            a = 1.0 + 0.2 * rng.standard_normal(shp)
+        elif name.endswith("side.norm"):
+            a = 0.3 + 0.05 * rng.standard_normal(shp)
+        elif ".mu." in name:
+            a = rng.random(shp)
+        elif last in ("b", "sink", "u", "dt_bias", "A_log") and len(shp) == 1 or last == "u":
+            a = 0.5 * rng.standard_normal(shp)
+        elif last == "w0":
+            a = -1.5 + rng.standard_normal(shp)
+        elif last == "rel":
+            a = rng.standard_normal(shp)
+        elif last == "conv":
+            a = 0.5 * rng.standard_normal(shp)
+        elif name in ("embed", "side.embed"):
+            a = rng.standard_normal(shp)
+        elif name == "pos":
+            a = 0.3 * rng.standard_normal(shp)
+        else:
+            a = rng.standard_normal(shp) / math.sqrt(shp[-1])
+        W[name] = bf16_round(a.astype(np.float32))
+    return W

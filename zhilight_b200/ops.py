@@ -587,3 +587,116 @@ def moe_route(x, w_router, correction, top, score_fn=MOE_SCORE_SIGMOID, renormal
     _lib.call("zl_moe_route", _p(x), d, _p(w_router), _p(correction), _p(te), _p(tw), _p(off), _p(lt), _p(lp), t, d, e, top,
               score_fn, int(renormalize), 0, _stream())
     return te, tw, off, lt, lp
+
+
+# ------------------------------------------------------------------ block attention with distance bias, predecessor mixes,
+# norm after the sum, gated delta rule, decaying state with a bonus
+GEMM_EPI_GEGLU_TANH, GEMM_EPI_GELU_TANH_MUL, GEMM_EPI_SOFTCAP = 5, 6, 7
+GATE_SIGMOID, GATE_SILU = 0, 1
+
+
+def gemm_nt_fused(x, w, bias=None, out_dtype=None, epilogue=GEMM_EPI_NONE, mul=None, limit=0.0):
+    """y = epi(x @ w^T + bias); epilogue none / relu^2 / tanh / gelu_tanh(v) * mul (mul (M, N) fp32) / gelu_tanh(gate) * up over
+    column pairs (y has N / 2 columns) / soft cap at `limit`."""
+    m, k = x.shape
+    n = w.shape[0]
+    n_out = n // 2 if epilogue == GEMM_EPI_GEGLU_TANH else n
+    y = torch.empty((m, n_out), dtype=out_dtype or x.dtype, device=x.device)
+    _lib.call("zl_gemm_nt_fused", _p(x), k, _p(w), k, _p(bias), _p(y), n_out, m, n, k, _dt(x), _dt(y), epilogue, _p(mul),
+              mul.shape[1] if mul is not None else 0, limit, 0, _stream())
+    return y
+
+
+def distance_bias_table(table, far, n_dist):
+    """table (rows, heads) numpy float32 -> (heads, n_dist) numpy float32: the table's row for every distance below n_dist."""
+    import numpy as np
+    t = np.ascontiguousarray(table, dtype=np.float32)
+    out = np.zeros((t.shape[1], n_dist), dtype=np.float32)
+    _lib.call("zl_distance_bias_table", t.ctypes.data_as(ctypes.c_void_p), t.shape[0], t.shape[1], float(far), n_dist,
+              out.ctypes.data_as(ctypes.c_void_p))
+    return out
+
+
+def sink_attention_local(q, k_table, v_table, slot, pos, scale, heads, kv_heads, dim, vdim, sink=None, chunk=0, dist_bias=None,
+                         splits=1, run_row0=None, run_len=None, max_run_len=0):
+    """sink_attention restricted to blocks of `chunk` positions (0: none) and with dist_bias (heads, n_dist) fp32 added to the
+    scaled scores by distance."""
+    t = q.shape[0]
+    lib = _lib.load()
+    nbytes = lib.zl_sink_attention_workspace_bytes(t, heads, vdim, splits)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
+    out = torch.empty((t, heads * vdim), dtype=q.dtype, device=q.device)
+    _lib.call("zl_sink_attention_local", _p(q), _p(k_table), _p(v_table), _p(slot), _p(pos), _p(sink), None, 0, scale, chunk,
+              _p(dist_bias), dist_bias.shape[1] if dist_bias is not None else 0, _p(out), t, heads, kv_heads, dim, vdim, splits,
+              _p(ws), nbytes, _p(run_row0), _p(run_len), run_row0.numel() if run_row0 is not None else 0, max_run_len, _dt(q), 0,
+              _stream())
+    return out
+
+
+def qk_fullnorm_append(proj, q_off, k_off, heads, kv_heads, dim, q_weight, k_weight, eps, k_table, v_table, slot, pos, dtype):
+    """proj (T, ld) fp32 -> q (T, heads * dim) of `dtype`, normed over the whole projection; the normed k goes to the key
+    cache rows (slot, pos), the projected k itself to the value cache rows."""
+    t, ldp = proj.shape
+    q = torch.empty((t, heads * dim), dtype=dtype, device=proj.device)
+    _lib.call("zl_qk_fullnorm_append", _p(proj), ldp, q_off, k_off, heads, kv_heads, dim, _p(q_weight), _p(k_weight), eps, _p(q),
+              _p(k_table), _p(v_table), _p(slot), _p(pos), t, _dt(q), 0, _stream())
+    return q
+
+
+def token_shift_mix(x, mu, state_table, slot, pos, store_state, out_dtype=torch.float32):
+    """x (T, D) fp32, mu (n, D) fp32 -> (n, T, D): x + (x_prev - x) * mu[s]; state (slots, D) fp32 through its pointer table."""
+    t, d = x.shape
+    n = mu.shape[0]
+    out = torch.empty((n, t, d), dtype=out_dtype, device=x.device)
+    _lib.call("zl_token_shift_mix", _p(x), d, _p(mu), n, _p(state_table), _p(slot), _p(pos), _p(out), t * d, t, d,
+              int(store_state), _dt(out), 0, _stream())
+    return out
+
+
+def store_run_tails(src, col, channels, n_tail, run_row0, run_len, slot, pos, ring_table):
+    _lib.call("zl_store_run_tails", _p(src), src.shape[1], col, channels, n_tail, _p(run_row0), _p(run_len), run_row0.numel(),
+              _p(slot), _p(pos), _p(ring_table), 0, _stream())
+
+
+def postnorm_combine(x, alpha, a, coef_a, weight, eps, b=None, coef_b=0.0, act_dtype=None):
+    """x (T, D) fp32 <- weight * rms(alpha x + coef_a a + coef_b b) in place; returns the new x rounded to act_dtype if given."""
+    t, d = x.shape
+    xa = torch.empty((t, d), dtype=act_dtype, device=x.device) if act_dtype is not None else None
+    _lib.call("zl_postnorm_combine", _p(x), d, alpha, _p(a), d, coef_a, _p(b), d, coef_b, _p(weight), _p(xa),
+              _dt(xa) if xa is not None else BF16, t, d, eps, 0, _stream())
+    return xa
+
+
+def head_rmsnorm_gate_fn(o, heads, vdim, eps, weight=None, weight_head_stride=0, gate=None, gate_fn=GATE_SIGMOID,
+                         out_dtype=torch.float32):
+    t = o.shape[0]
+    y = torch.empty((t, heads * vdim), dtype=out_dtype, device=o.device)
+    _lib.call("zl_head_rmsnorm_gate_fn", _p(o), heads * vdim, _p(weight), weight_head_stride, _p(gate), heads * vdim, gate_fn, _p(y),
+              heads * vdim, t, heads, vdim, eps, _dt(y), 0, _stream())
+    return y
+
+
+def gated_delta_rule(proj, col_qkv, col_rate, col_decay, conv_weight, a_log, dt_bias, unit_eps, q_scale, ring_table, run_row0,
+                     run_len, slot, pos, state_table, heads, kv_heads, dim_k, dim_v):
+    """proj (T, ld) fp32 (q | k | v from col_qkv, rate logits, decay inputs); states and rings are updated in place through
+    their pointer tables.  -> o (T, heads * dim_v) fp32."""
+    t, ld = proj.shape
+    o = torch.empty((t, heads * dim_v), dtype=torch.float32, device=proj.device)
+    nbytes = _lib.load().zl_delta_rule_workspace_bytes(t, heads, dim_k, dim_v)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=proj.device)
+    _lib.call("zl_gated_delta_rule", _p(proj), ld, col_qkv, col_rate, col_decay, _p(conv_weight), conv_weight.shape[1], _p(a_log),
+              _p(dt_bias), unit_eps, q_scale, _p(ring_table), _p(run_row0), _p(run_len), run_row0.numel(), _p(slot), _p(pos),
+              _p(state_table), _p(o), heads * dim_v, heads, kv_heads, dim_k, dim_v, t, _p(ws), nbytes, 0, _stream())
+    return o
+
+
+def bonus_decay_scan(r, k, v, decay_logit, bonus, run_row0, run_len, slot, pos, state_table, heads, dim_k, dim_v):
+    """r, k, decay_logit (T, heads * dim_k), v (T, heads * dim_v) fp32, bonus (heads, dim_k) fp32 -> o (T, heads * dim_v)."""
+    t = r.shape[0]
+    o = torch.empty((t, heads * dim_v), dtype=torch.float32, device=r.device)
+    nbytes = _lib.load().zl_delta_rule_workspace_bytes(t, heads, dim_k, dim_v)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=r.device)
+    _lib.call("zl_bonus_decay_scan", _p(r), heads * dim_k, _p(k), heads * dim_k, _p(v), heads * dim_v, _p(decay_logit),
+              heads * dim_k, _p(bonus), _p(run_row0), _p(run_len), run_row0.numel(), _p(slot), _p(pos), _p(state_table), _p(o),
+              heads * dim_v, heads, dim_k, dim_v, t, _p(ws), nbytes, 0, _stream())
+    return o
