@@ -569,6 +569,124 @@ def run_compare_kodupel(args):
                       "timing": "CUDA events on the model's stream; weights per pass larger than L2"}))
 
 
+# ----------------------------------------------------------------------------------------------------------------------
+# --compare-lagelorn: prefill and decode throughput of the Lagelorn family beside Kodupel (the closest existing model:
+# the same attention, recurrence and GEMM kernels, an fp32 residual stream) at equal width, depth, heads and (nearly) equal
+# active Linear parameters per token, random weights.  Does not touch the default workload.
+# ----------------------------------------------------------------------------------------------------------------------
+def _lagelorn_config(sz):
+    D = sz["width"]
+    left = dict(heads=sz["heads"], kv_heads=8, dim=sz["dim"], vdim=sz["dim"], scale=sz["dim"] ** -0.5, bias_max=4096.0,
+                mask={"size": 1024})
+    par = {"left": left, "right": dict(heads=sz["delta_heads"], dim=sz["delta_dim"]), "left_scale": 0.7, "right_scale": 0.7}
+    mlp = {"kind": "dense", "ff": sz["ff"]}
+    layers = []
+    for i in range(sz["layers"]):
+        if i % 4 == 2:
+            layers.append({"type": "delta", "mlp": mlp,
+                           "mixer": dict(heads=sz["delta_heads"], kv_heads=sz["delta_heads"] // 2, dim=sz["delta_dim"],
+                                         vdim=sz["delta_dim"], conv=4)})
+        else:
+            layers.append({"type": "parallel", "mixer": par, "mlp": mlp})
+    return {"architecture": "Lagelorn", "vocab": sz["vocab"], "width": D, "max_positions": 8192, "layers": layers,
+            "norm": {"eps": 1e-6}, "postln_alpha": 2.0, "token_side": {"dim": 256}, "logit_softcap": 30.0}
+
+
+def _lagelorn_params(sz):
+    """(Linear parameters one token uses = parameters a step reads, cache bytes per cached position inside a block, state
+    bytes per request and step)."""
+    D, H, d, F, sd = sz["width"], sz["heads"], sz["dim"], sz["ff"], 256
+    hd = sz["delta_heads"] * sz["delta_dim"]
+    active = cache = state = 0
+    for i in range(sz["layers"]):
+        if i % 4 == 2:
+            G = sz["delta_heads"] // 2
+            mix = D * (2 * G * sz["delta_dim"] + 2 * hd + 2 * sz["delta_heads"]) + hd * D
+            state += 2 * sz["delta_heads"] * sz["delta_dim"] ** 2 * 4
+        else:
+            mix = D * (H + 8) * d + H * d * D + 4 * hd * D + 64 * (D + hd) + hd * D
+            cache += 2 * 8 * d * 2
+            state += 2 * sz["delta_heads"] * sz["delta_dim"] ** 2 * 4
+        active += mix + 3 * D * F + 2 * D * sd
+    return active + sz["vocab"] * D, cache, state
+
+
+def run_compare_lagelorn(args):
+    import numpy as np
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    torch.cuda.set_device(0)
+    from zhilight_b200 import build
+    build.build()
+    from zhilight_b200.kodupel import KodupelDecoder
+    from zhilight_b200.lagelorn import LagelornDecoder
+    hbm, how = read_peaks()
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    tflops = json.load(open(peaks_path))["bf16_tflops"] if os.path.exists(peaks_path) else 1590.0
+    ctx, chunk, n_prompt = args.prompt if args.prompt > 128 else 1024, 1024, 2048
+    steps, warm = max(args.steps, 16), max(args.warmup, 3)
+    rng = np.random.default_rng(0)
+    rows = []
+    sampler = ClockSampler(0)
+    sampler.start()
+    sampler.mark_region_start()
+    for name, sz in KODUPEL_SIZES.items():
+        if args.compare_sizes and name not in args.compare_sizes.split(","):
+            continue
+        for kind in [k for k in ("lagelorn", "kodupel") if k in args.compare_models.split(",")]:
+            max_seq = max(ctx, n_prompt) + 4 * (steps + warm) + 64
+            kw = dict(dtype="bf16", max_batch=32, max_seq=max_seq, max_step_tokens=chunk, use_pdl=not args.no_pdl,
+                      use_graph=not args.no_graph)
+            if kind == "lagelorn":
+                dec = LagelornDecoder.from_config_dict(_lagelorn_config(sz), **kw)
+            else:
+                dec = KodupelDecoder.from_config_dict(_kodupel_config(sz), **kw)
+            dec.init_synthetic(seed=1)
+            stream = torch.cuda.ExternalStream(dec.stream())
+            out = {"size": name, "model": kind}
+            toks = rng.integers(0, sz["vocab"], n_prompt).astype(np.int32)
+            for _ in range(2):
+                dec.prefill(0, toks, 0)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(3):
+                dec.prefill(0, toks, 0)
+            e1.record(stream)
+            e1.synchronize()
+            ms = e0.elapsed_time(e1) / 3
+            active = _lagelorn_params(sz)[0] if kind == "lagelorn" else _kodupel_params(sz, 1)[0]
+            out["linear_params_per_token"] = int(active)
+            flops = 2.0 * (active - sz["vocab"] * sz["width"]) * n_prompt
+            out["prefill"] = {"tokens": n_prompt, "chunk": chunk, "ms": round(ms, 3), "tok_s": round(n_prompt / ms * 1e3),
+                              "linear_tflops": round(flops / ms / 1e9, 1),
+                              "of_measured_bf16_peak": round(flops / ms / 1e9 / tflops, 4)}
+            for b in range(32):
+                dec.prefill(b, toks[:ctx], 0)
+            for B in (1, 32):
+                dec.set_state(rng.integers(0, sz["vocab"], B).astype(np.int32), np.full(B, ctx, dtype=np.int32))
+                ms, _ = measure_decode(dec, B, steps, warm, stream, torch.cuda.synchronize)
+                mid = ctx + warm + steps // 2
+                if kind == "lagelorn":
+                    read, cache, state = _lagelorn_params(sz)
+                    step_bytes = read * 2 + B * ((mid % 1024 + 1) * cache + state)     # a token reads its own block only
+                else:
+                    _, read, cache, state = _kodupel_params(sz, B)
+                    step_bytes = read * 2 + B * (mid * cache + state)
+                out["decode_b%d" % B] = {"ctx": ctx, "ms_per_step": round(ms / steps, 4), "tok_s": round(B * steps / ms * 1e3, 1),
+                                          "step_bytes": int(step_bytes),
+                                          "of_%s_hbm_peak" % how: round(step_bytes / (ms / steps * 1e-3) / 1e9 / hbm, 4)}
+            out["kernels_per_step"] = dec.stats()[1]
+            dec.close()
+            del dec
+            torch.cuda.empty_cache()
+            rows.append(out)
+            print(json.dumps(out), file=sys.stderr, flush=True)
+    clocks = sampler.finish()
+    print(json.dumps({"compare": "lagelorn vs kodupel (bf16, random weights, synthetic tokens)", "rows": rows, "clocks": clocks,
+                      "timing": "CUDA events on the model's stream; weights per pass larger than L2"}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -595,11 +713,18 @@ def main():
     ap.add_argument("--compare-sizes", default="", help="--compare-kodupel: comma-separated subset of its layer sizes")
     ap.add_argument("--compare-kodupel", action="store_true",
                     help="instead of the default workload: Kodupel beside the bf16 Llama decoder at a few layer sizes")
+    ap.add_argument("--compare-lagelorn", action="store_true",
+                    help="instead of the default workload: Lagelorn beside Kodupel at a few layer sizes")
     ap.add_argument("--compare-dekipel", action="store_true",
                     help="instead of the default workload: Dekipel beside the bf16 Llama decoder at a few layer sizes")
     args = ap.parse_args()
     if args.compare_dekipel:
         run_compare_dekipel(args)
+        return
+    if args.compare_lagelorn:
+        if args.compare_models == "dekipel,llama":
+            args.compare_models = "lagelorn,kodupel"
+        run_compare_lagelorn(args)
         return
     if args.compare_kodupel:
         if args.compare_models == "dekipel,llama":

@@ -253,20 +253,25 @@ struct GatedPrepP {
 
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
-// one CTA per token: convolution + silu of every channel into shared memory, then a warp per head writes the token vectors
-__global__ void __launch_bounds__(256) k_gated_delta_prep(GatedPrepP p) {
-    extern __shared__ float gsm[];   // C
+// One CTA per (token, q / k head): convolution + silu of that head's q and k channels and of the v channels of the value
+// heads that use it into shared memory, then a warp per value head writes the token vectors.  No channel is shared between
+// CTAs, so a channel's ring entries are read and (store_ring) overwritten by one thread.  grid (T, G)
+__global__ void __launch_bounds__(128) k_gated_delta_prep(GatedPrepP p) {
+    extern __shared__ float gsm[];   // q (dk) | k (dk) | v (rep * dv)
     pdl_trigger();
     pdl_wait();
-    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int C = 2 * p.G * p.dk + p.H * p.dv, nr = p.taps - 1;
+    const int t = blockIdx.x, g = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int dk = p.dk, rep = p.H / p.G, nr = p.taps - 1;
+    const int C = 2 * p.G * dk + p.H * p.dv, n_mine = 2 * dk + rep * p.dv;
     const int sl = p.slot[t], pos = p.pos[t];
     const float* row = p.proj + (size_t)t * p.ld + p.col_qkv;
     float* ring = nr > 0 ? static_cast<float*>(p.ring_addrs[sl]) : nullptr;
     // how many earlier rows of this step belong to the same sequence (at most taps - 1 matter)
     int back = 0;
     while (back < nr && t - back - 1 >= 0 && p.slot[t - back - 1] == sl) ++back;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    for (int i = threadIdx.x; i < n_mine; i += blockDim.x) {
+        // local index -> channel among q | k | v of all heads
+        const int c = i < dk ? g * dk + i : (i < 2 * dk ? p.G * dk + g * dk + (i - dk) : 2 * p.G * dk + g * rep * p.dv + (i - 2 * dk));
         const float* w = p.conv_w + (size_t)c * p.taps;
         const float cur = row[c];
         float acc = w[nr] * cur;
@@ -277,19 +282,18 @@ __global__ void __launch_bounds__(256) k_gated_delta_prep(GatedPrepP p) {
             acc = fmaf(w[nr - j], xin, acc);
         }
         if (p.store_ring && nr > 0) ring[(size_t)(pos % nr) * C + c] = cur;
-        gsm[c] = silu_f(acc);
+        gsm[i] = silu_f(acc);
     }
     __syncthreads();
-    const int dk = p.dk, rep = p.H / p.G;
-    for (int h = warp; h < p.H; h += (int)(blockDim.x >> 5)) {
-        const int g = h / rep;
-        const float* q = gsm + (size_t)g * dk;
-        const float* k = gsm + (size_t)(p.G + g) * dk;
-        const float* v = gsm + (size_t)2 * p.G * dk + (size_t)h * p.dv;
-        float sq = 0.f, sk = 0.f;
-        for (int i = lane; i < dk; i += 32) sq = fmaf(q[i], q[i], sq), sk = fmaf(k[i], k[i], sk);
-        const float iq = p.q_scale / sqrtf(warp_sum(sq) + p.unit_eps), ik = 1.0f / sqrtf(warp_sum(sk) + p.unit_eps);
-        const float* prow = p.proj + (size_t)t * p.ld;
+    const float* q = gsm;
+    const float* k = gsm + dk;
+    float sq = 0.f, sk = 0.f;
+    for (int i = lane; i < dk; i += 32) sq = fmaf(q[i], q[i], sq), sk = fmaf(k[i], k[i], sk);
+    const float iq = p.q_scale / sqrtf(warp_sum(sq) + p.unit_eps), ik = 1.0f / sqrtf(warp_sum(sk) + p.unit_eps);
+    const float* prow = p.proj + (size_t)t * p.ld;
+    for (int hh = warp; hh < rep; hh += (int)(blockDim.x >> 5)) {
+        const int h = g * rep + hh;
+        const float* v = gsm + 2 * dk + (size_t)hh * p.dv;
         const float beta = 1.0f / (1.0f + expf(-prow[p.col_b + h]));
         const float decay = expf(-expf(p.a_log[h]) * softplus_f(prow[p.col_a + h] + p.dt_bias[h]));
         float* tv = p.prep + ((size_t)t * p.H + h) * (5 * dk + p.dv);
@@ -406,11 +410,11 @@ extern "C" int zl_gated_delta_rule(const float* proj, long long ld, int col_qkv,
     ZL_CHECK_ARG(taps >= 1 && (taps == 1 || ring_addrs) && heads > 0 && kv_heads > 0 && heads % kv_heads == 0);
     ZL_CHECK_ARG(runs > 0 && runs <= 65535 && heads <= 65535 && dim_k > 0 && dim_v > 0);
     ZL_CHECK_ARG(T > 0 && T <= 65535 && workspace && workspace_bytes >= zl_delta_rule_workspace_bytes(T, heads, dim_k, dim_v));
-    const int C = 2 * kv_heads * dim_k + heads * dim_v;
-    ZL_CHECK_SUPPORTED((size_t)C * 4 <= 200 * 1024);
+    const int C = 2 * kv_heads * dim_k + heads * dim_v, n_cta = 2 * dim_k + heads / kv_heads * dim_v;
+    ZL_CHECK_SUPPORTED((size_t)n_cta * 4 <= 200 * 1024 && kv_heads <= 65535);
     GatedPrepP g{proj, ld, col_qkv, col_rate, col_decay, heads, kv_heads, dim_k, dim_v, taps, conv_weight, a_log, dt_bias,
                  ring_addrs, slot, pos, unit_eps, q_scale, runs == T ? 1 : 0, static_cast<float*>(workspace)};
-    const size_t smem = (size_t)C * 4;
+    const size_t smem = (size_t)n_cta * 4;
     if (smem > 48 * 1024) {
         static size_t set_for = 0;
         if (smem > set_for) {
@@ -418,7 +422,7 @@ extern "C" int zl_gated_delta_rule(const float* proj, long long ld, int col_qkv,
             set_for = smem;
         }
     }
-    ZL_CHECK_CUDA(launch(k_gated_delta_prep, dim3(T), dim3(256), smem, stream, pdl != 0, g));
+    ZL_CHECK_CUDA(launch(k_gated_delta_prep, dim3(T, kv_heads), dim3(128), smem, stream, pdl != 0, g));
     if (runs != T && taps > 1)   // rows of a run read ring entries that its last rows overwrite: stored afterwards
         if (int rc_ = (zl_store_run_tails(proj, ld, col_qkv, C, taps - 1, run_row0, run_len, runs, slot, pos, ring_addrs, pdl, stream))) return rc_;
     DeltaP p{nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0, run_row0, run_len, slot, pos, state_addrs, o, ld_o,

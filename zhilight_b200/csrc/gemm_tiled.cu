@@ -33,6 +33,7 @@ struct GemmP {
     float limit = 0.f, alpha = 1.f, beta = 0.f;   // gated unit: g = min(gate, limit), u = clamp(up, +-limit), g sigmoid(alpha g) (u + beta)
                                       // soft cap: limit * tanh(v / limit)
     int pair_gelu = 0;                // few-rows kernel with a gated unit: gelu_tanh(gate) * up instead of the clamped unit
+    int act_gelu_mul = 0;             // few-rows kernel without the gated unit: gelu_tanh of the (biased) sum times gate[m][n]
 };
 
 __host__ __device__ constexpr bool epi_pairs(int epi) { return epi == ZL_GEMM_EPI_GLU_CLAMP || epi == ZL_GEMM_EPI_GEGLU_TANH; }
@@ -252,16 +253,23 @@ __global__ void __launch_bounds__(256) k_gemm_small_m(GemmP p) {
 #pragma unroll
         for (int m = 0; m < MT; ++m) acc[m] = 0.f;
         const T* wr = w + (size_t)n * p.ldw;
-        for (int k8 = lane; k8 < K8; k8 += 32) {
-            float wf[8];
-            unpack8<T>(ld_nc_na_u4(wr + k8 * 8), wf);
+        for (int k8 = lane; k8 < K8; k8 += 128) {   // four 16-byte loads of the weight row in flight per lane
+            uint4 wq[4];
 #pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                if (m < p.M) {
-                    float xf[8];
-                    unpack8<T>(*reinterpret_cast<const uint4*>(sx + (size_t)m * K + k8 * 8), xf);
+            for (int u = 0; u < 4; ++u) wq[u] = k8 + 32 * u < K8 ? ld_nc_na_u4(wr + (size_t)(k8 + 32 * u) * 8) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[m] = fmaf(wf[e], xf[e], acc[m]);
+            for (int u = 0; u < 4; ++u) {
+                if (k8 + 32 * u >= K8) break;
+                float wf[8];
+                unpack8<T>(wq[u], wf);
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    if (m < p.M) {
+                        float xf[8];
+                        unpack8<T>(*reinterpret_cast<const uint4*>(sx + (size_t)m * K + (size_t)(k8 + 32 * u) * 8), xf);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) acc[m] = fmaf(wf[e], xf[e], acc[m]);
+                    }
                 }
             }
         }
@@ -369,6 +377,7 @@ __global__ void __launch_bounds__(256) k_gemm_grouped_small(GemmP p) {
                 } else {
                     if (p.bias) v += p.bias[(size_t)b * p.bb + n];
                     if (p.act_tanh) v = tanhf(v);
+                    if (p.act_gelu_mul && m < mc) v = gelu_f(v) * p.gate[(size_t)(first + m0 + m) * p.ldg + n];
                 }
                 if (lane == m) mine = v;
             }
@@ -577,9 +586,12 @@ static int gemm_dispatch(GemmP p, int batch, int in_dtype, int out_dtype, int ep
         else
             e = out_dtype == ZL_F32 ? launch_grouped_small<__half, float>(p, 1, true, pdl != 0, stream)
                                     : launch_grouped_small<__half, __half>(p, 1, true, pdl != 0, stream);
-    } else if (!grouped && epilogue == ZL_GEMM_EPI_TANH && batch == 1 && M <= 8 && vx && vw && K % 8 == 0 &&
-               (size_t)8 * K * 2 <= 160 * 1024) {   // a narrow tanh projection of a decode step: one column per warp, loads in flight
-        p.act_tanh = 1;
+    } else if (!grouped && (epilogue == ZL_GEMM_EPI_TANH || epilogue == ZL_GEMM_EPI_GELU_TANH_MUL) && batch == 1 &&
+               (M <= 8 || (M <= 32 && N <= 512)) && vx && vw && K % 8 == 0 && (size_t)8 * K * 2 <= 160 * 1024) {
+        // a narrow tanh / gelu-times-multiplier projection of a decode step: one column per warp, loads in flight (a tile
+        // kernel would put a handful of CTAs on it)
+        p.act_tanh = epilogue == ZL_GEMM_EPI_TANH;
+        p.act_gelu_mul = epilogue == ZL_GEMM_EPI_GELU_TANH_MUL;
         if (in_dtype == ZL_BF16)
             e = out_dtype == ZL_F32 ? launch_grouped_small<__nv_bfloat16, float>(p, 1, false, pdl != 0, stream)
                                     : launch_grouped_small<__nv_bfloat16, __nv_bfloat16>(p, 1, false, pdl != 0, stream);

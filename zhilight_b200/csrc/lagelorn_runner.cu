@@ -112,12 +112,15 @@ __global__ void k_embed_pos_side(const int32_t* __restrict__ ids, const int32_t*
     int id = ids[blockIdx.x], p = pos[blockIdx.x];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
     p = p < 0 ? 0 : (p >= max_pos ? max_pos - 1 : p);
+    if (blockIdx.y == 1) {   // grid (T, 2): the second CTA of a token gathers the side row
+        for (int i = threadIdx.x; i < S; i += blockDim.x) side[(size_t)blockIdx.x * S + i] = to_f32<TW>(side_table[(size_t)id * S + i]);
+        return;
+    }
     for (int i = threadIdx.x; i < D; i += blockDim.x) {
         const float v = to_f32<TW>(table[(size_t)id * D + i]) + to_f32<TW>(pos_table[(size_t)p * D + i]);
         x[(size_t)blockIdx.x * D + i] = v;
         if (xa) xa[(size_t)blockIdx.x * D + i] = from_f32<TW>(v);
     }
-    for (int i = threadIdx.x; i < S; i += blockDim.x) side[(size_t)blockIdx.x * S + i] = to_f32<TW>(side_table[(size_t)id * S + i]);
 }
 
 // dst rows 2j / 2j+1 <- gate / up row j; src are (ff, D) each
@@ -397,11 +400,11 @@ int enqueue_step(zl_lagelorn* m, int T, int n_want, int n_runs, int max_run, int
     void* xa_out = dt == ZL_F32 ? nullptr : m->xa;
     const bool single = n_runs == T;   // every row is a run of its own
     if (dt == ZL_F32) {
-        ZL_CHECK_CUDA(launch(k_embed_pos_side<float>, dim3(T), dim3(128), 0, st, false, (const int32_t*)m->d_tokens,
+        ZL_CHECK_CUDA(launch(k_embed_pos_side<float>, dim3(T, 2), dim3(256), 0, st, false, (const int32_t*)m->d_tokens,
                              (const int32_t*)m->d_pos, (const float*)m->embed, (const float*)m->pos_table,
                              (const float*)m->side_embed, m->x, (float*)nullptr, m->side, D, S, c.vocab, c.max_positions));
     } else {
-        ZL_CHECK_CUDA(launch(k_embed_pos_side<__nv_bfloat16>, dim3(T), dim3(128), 0, st, false, (const int32_t*)m->d_tokens,
+        ZL_CHECK_CUDA(launch(k_embed_pos_side<__nv_bfloat16>, dim3(T, 2), dim3(256), 0, st, false, (const int32_t*)m->d_tokens,
                              (const int32_t*)m->d_pos, (const __nv_bfloat16*)m->embed, (const __nv_bfloat16*)m->pos_table,
                              (const __nv_bfloat16*)m->side_embed, m->x, (__nv_bfloat16*)m->xa, m->side, D, S, c.vocab,
                              c.max_positions));

@@ -182,78 +182,136 @@ __global__ void __launch_bounds__(256) k_rmsnorm_residual_combine(const float* _
     }
 }
 
-// one CTA per token: q <- rms(q over all H*d) * q_w -> q_out; k <- rms(k over all G*d) * k_w -> key cache row; the
-// projected k itself -> value cache row
+// grid (T, 2).  CTA (t, 0): q <- rms(q over all H*d) * q_w -> q_out.  CTA (t, 1): k <- rms(k over all G*d) * k_w -> key cache
+// row; the projected k itself -> value cache row.  A thread keeps up to 8 of its values in registers between the two passes.
 template <typename TO>
-__global__ void __launch_bounds__(256) k_qk_fullnorm_append(const float* __restrict__ proj, long long ldp, int q_off, int k_off,
+__global__ void __launch_bounds__(512) k_qk_fullnorm_append(const float* __restrict__ proj, long long ldp, int q_off, int k_off,
                                                             int nq, int nk, const float* __restrict__ q_w,
                                                             const float* __restrict__ k_w, float eps, TO* __restrict__ q_out,
                                                             void* const* k_addrs, void* const* v_addrs,
                                                             const int32_t* __restrict__ slot, const int32_t* __restrict__ pos) {
-    __shared__ float red[2][8];
+    __shared__ float red[16];
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
-    const float* q = proj + (size_t)t * ldp + q_off;
-    const float* k = proj + (size_t)t * ldp + k_off;
-    float sq = 0.f, sk = 0.f;
-    for (int c = threadIdx.x; c < nq; c += blockDim.x) sq = fmaf(q[c], q[c], sq);
-    for (int c = threadIdx.x; c < nk; c += blockDim.x) sk = fmaf(k[c], k[c], sk);
-    sq = warp_sum(sq), sk = warp_sum(sk);
-    if ((threadIdx.x & 31) == 0) red[0][threadIdx.x >> 5] = sq, red[1][threadIdx.x >> 5] = sk;
+    const bool keys = blockIdx.y == 1;
+    const int n = keys ? nk : nq;
+    const float* src = proj + (size_t)t * ldp + (keys ? k_off : q_off);
+    const float* w = keys ? k_w : q_w;
+    float keep[8], ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int c = threadIdx.x + i * 512;
+        keep[i] = c < n ? src[c] : 0.f;
+        ss = fmaf(keep[i], keep[i], ss);
+    }
+    for (int c = threadIdx.x + 8 * 512; c < n; c += 512) ss = fmaf(src[c], src[c], ss);
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
     __syncthreads();
-    float tq = 0.f, tk = 0.f;
-    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tq += red[0][i], tk += red[1][i];
-    const float rq = 1.0f / sqrtf(tq / (float)nq + eps), rk = 1.0f / sqrtf(tk / (float)nk + eps);
-    TO* kd = static_cast<TO*>(k_addrs[slot[t]]) + (size_t)pos[t] * nk;
-    TO* vd = static_cast<TO*>(v_addrs[slot[t]]) + (size_t)pos[t] * nk;
-    for (int c = threadIdx.x; c < nq; c += blockDim.x) q_out[(size_t)t * nq + c] = from_f32<TO>(q[c] * rq * q_w[c]);
-    for (int c = threadIdx.x; c < nk; c += blockDim.x) {
-        kd[c] = from_f32<TO>(k[c] * rk * k_w[c]);
-        vd[c] = from_f32<TO>(k[c]);
+    float tot = 0.f;
+    for (int i = 0; i < 16; ++i) tot += red[i];
+    const float r = 1.0f / sqrtf(tot / (float)n + eps);
+    TO* dst = keys ? static_cast<TO*>(k_addrs[slot[t]]) + (size_t)pos[t] * nk : q_out + (size_t)t * nq;
+    TO* vd = keys ? static_cast<TO*>(v_addrs[slot[t]]) + (size_t)pos[t] * nk : nullptr;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int c = threadIdx.x + i * 512;
+        if (c < n) {
+            dst[c] = from_f32<TO>(keep[i] * r * w[c]);
+            if (keys) vd[c] = from_f32<TO>(keep[i]);
+        }
+    }
+    for (int c = threadIdx.x + 8 * 512; c < n; c += 512) {
+        dst[c] = from_f32<TO>(src[c] * r * w[c]);
+        if (keys) vd[c] = from_f32<TO>(src[c]);
     }
 }
 
-// one CTA per token: out[s][t] = x[t] + (prev - x[t]) * mu[s], s < n_mix; prev = x[t - 1] when that row belongs to the same
-// sequence, zeros at position 0, else the slot's stored last token.  store_state: every row is a run of its own, so the
-// kernel also stores x[t] as the slot's last token (otherwise the caller stores the runs' tails afterwards).
-template <typename TO>
+// out[s][t] = x[t] + (prev - x[t]) * mu[s], s < n_mix; prev = x[t - 1] when that row belongs to the same sequence, zeros at
+// position 0, else the slot's stored last token.  store_state: every row is a run of its own, so the kernel also stores
+// x[t] as the slot's last token (otherwise the caller stores the runs' tails afterwards).  grid (T, ceil(D / (256 * V)));
+// a thread owns V consecutive channels (V = 4 when the rows are 16-byte aligned), read once and written n_mix times.
+template <typename TO, int V>
 __global__ void __launch_bounds__(256) k_token_shift_mix(const float* __restrict__ x, long long ldx, const float* __restrict__ mu,
                                                          int n_mix, void* const* state_addrs, const int32_t* __restrict__ slot,
                                                          const int32_t* __restrict__ pos, TO* __restrict__ out, long long out_stride,
                                                          int D, int store_state) {
     pdl_trigger();
     pdl_wait();
-    const int t = blockIdx.x, sl = slot[t];
+    const int t = blockIdx.x, sl = slot[t], c = (blockIdx.y * 256 + threadIdx.x) * V;
+    if (c >= D) return;
     const bool in_step = t > 0 && slot[t - 1] == sl, first = pos[t] == 0;
     float* st = static_cast<float*>(state_addrs[sl]);
     const float* xr = x + (size_t)t * ldx;
-    for (int c = threadIdx.x; c < D; c += blockDim.x) {
-        const float cur = xr[c];
-        const float prev = in_step ? xr[c - ldx] : (first ? 0.f : st[c]);
-        const float dx = prev - cur;
-        for (int s = 0; s < n_mix; ++s) out[(size_t)s * out_stride + (size_t)t * D + c] = from_f32<TO>(fmaf(dx, mu[(size_t)s * D + c], cur));
-        if (store_state) st[c] = cur;
+    float cur[V], dx[V];
+    if constexpr (V == 4) {
+        const float4 cv = *reinterpret_cast<const float4*>(xr + c);
+        float4 pv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (in_step) pv = *reinterpret_cast<const float4*>(xr + c - ldx);
+        else if (!first) pv = *reinterpret_cast<const float4*>(st + c);
+        cur[0] = cv.x, cur[1] = cv.y, cur[2] = cv.z, cur[3] = cv.w;
+        dx[0] = pv.x - cv.x, dx[1] = pv.y - cv.y, dx[2] = pv.z - cv.z, dx[3] = pv.w - cv.w;
+        if (store_state) *reinterpret_cast<float4*>(st + c) = cv;
+    } else {
+        cur[0] = xr[c];
+        dx[0] = (in_step ? xr[c - ldx] : (first ? 0.f : st[c])) - cur[0];
+        if (store_state) st[c] = cur[0];
+    }
+#pragma unroll 5
+    for (int s = 0; s < n_mix; ++s) {
+        TO* o = out + (size_t)s * out_stride + (size_t)t * D + c;
+        if constexpr (V == 4) {
+            const float4 m = *reinterpret_cast<const float4*>(mu + (size_t)s * D + c);
+            o[0] = from_f32<TO>(fmaf(dx[0], m.x, cur[0])), o[1] = from_f32<TO>(fmaf(dx[1], m.y, cur[1]));
+            o[2] = from_f32<TO>(fmaf(dx[2], m.z, cur[2])), o[3] = from_f32<TO>(fmaf(dx[3], m.w, cur[3]));
+        } else {
+            o[0] = from_f32<TO>(fmaf(dx[0], mu[(size_t)s * D + c], cur[0]));
+        }
     }
 }
 
-// one CTA per token: x <- w * s / sqrt(mean(s^2) + eps), s = alpha x + ca a + cb b (b may be null); also x rounded to TO
+// one CTA per token: x <- w * s / sqrt(mean(s^2) + eps), s = alpha x + ca a + cb b (b may be null); also x rounded to TO.
+// vec: D % 4 == 0, D <= 4096, 16-byte aligned rows: every thread keeps its (up to four) 4-channel sums in registers;
+// otherwise the sums wait in shared memory (D floats).
 template <typename TO>
 __global__ void __launch_bounds__(256) k_postnorm_combine(float* __restrict__ x, long long ldx, float alpha,
                                                           const float* __restrict__ a, long long lda, float ca,
                                                           const float* __restrict__ b, long long ldb, float cb,
-                                                          const float* __restrict__ w, TO* __restrict__ x_act, int D, float eps) {
-    extern __shared__ float psm[];   // D
+                                                          const float* __restrict__ w, TO* __restrict__ x_act, int D, float eps,
+                                                          int vec) {
+    extern __shared__ float psm[];   // D when !vec
     __shared__ float red[8];
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < D; c += blockDim.x) {
-        float s = fmaf(ca, a[(size_t)t * lda + c], alpha * x[(size_t)t * ldx + c]);
-        if (b) s = fmaf(cb, b[(size_t)t * ldb + c], s);
-        psm[c] = s;
-        ss = fmaf(s, s, ss);
+    float4 keep[4];
+    if (vec) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = (threadIdx.x + i * 256) * 4;
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < D) {
+                const float4 xv = *reinterpret_cast<const float4*>(x + (size_t)t * ldx + c);
+                const float4 av = *reinterpret_cast<const float4*>(a + (size_t)t * lda + c);
+                s.x = fmaf(ca, av.x, alpha * xv.x), s.y = fmaf(ca, av.y, alpha * xv.y);
+                s.z = fmaf(ca, av.z, alpha * xv.z), s.w = fmaf(ca, av.w, alpha * xv.w);
+                if (b) {
+                    const float4 bv = *reinterpret_cast<const float4*>(b + (size_t)t * ldb + c);
+                    s.x = fmaf(cb, bv.x, s.x), s.y = fmaf(cb, bv.y, s.y), s.z = fmaf(cb, bv.z, s.z), s.w = fmaf(cb, bv.w, s.w);
+                }
+            }
+            keep[i] = s;
+            ss = fmaf(s.x, s.x, fmaf(s.y, s.y, fmaf(s.z, s.z, fmaf(s.w, s.w, ss))));
+        }
+    } else {
+        for (int c = threadIdx.x; c < D; c += blockDim.x) {
+            float s = fmaf(ca, a[(size_t)t * lda + c], alpha * x[(size_t)t * ldx + c]);
+            if (b) s = fmaf(cb, b[(size_t)t * ldb + c], s);
+            psm[c] = s;
+            ss = fmaf(s, s, ss);
+        }
     }
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
@@ -261,6 +319,21 @@ __global__ void __launch_bounds__(256) k_postnorm_combine(float* __restrict__ x,
     float tot = 0.f;
     for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
     const float r = 1.0f / sqrtf(tot / (float)D + eps);
+    if (vec) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = (threadIdx.x + i * 256) * 4;
+            if (c >= D) continue;
+            const float4 wv = *reinterpret_cast<const float4*>(w + c);
+            const float4 nx = make_float4(keep[i].x * r * wv.x, keep[i].y * r * wv.y, keep[i].z * r * wv.z, keep[i].w * r * wv.w);
+            *reinterpret_cast<float4*>(x + (size_t)t * ldx + c) = nx;
+            if (x_act) {
+                x_act[(size_t)t * D + c] = from_f32<TO>(nx.x), x_act[(size_t)t * D + c + 1] = from_f32<TO>(nx.y);
+                x_act[(size_t)t * D + c + 2] = from_f32<TO>(nx.z), x_act[(size_t)t * D + c + 3] = from_f32<TO>(nx.w);
+            }
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
         const float nx = psm[c] * r * w[c];
         x[(size_t)t * ldx + c] = nx;
@@ -282,13 +355,13 @@ extern "C" int zl_qk_fullnorm_append(const float* proj, long long ldp, int q_off
     const int nq = heads * dim, nk = kv_heads * dim;
     cudaError_t e;
     if (dtype == ZL_F32)
-        e = launch(k_qk_fullnorm_append<float>, dim3(T), dim3(256), 0, stream, pdl != 0, proj, ldp, q_off, k_off, nq, nk, q_weight,
+        e = launch(k_qk_fullnorm_append<float>, dim3(T, 2), dim3(512), 0, stream, pdl != 0, proj, ldp, q_off, k_off, nq, nk, q_weight,
                    k_weight, eps, (float*)q_out, k_addrs, v_addrs, slot, pos);
     else if (dtype == ZL_BF16)
-        e = launch(k_qk_fullnorm_append<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, pdl != 0, proj, ldp, q_off, k_off, nq, nk,
+        e = launch(k_qk_fullnorm_append<__nv_bfloat16>, dim3(T, 2), dim3(512), 0, stream, pdl != 0, proj, ldp, q_off, k_off, nq, nk,
                    q_weight, k_weight, eps, (__nv_bfloat16*)q_out, k_addrs, v_addrs, slot, pos);
     else
-        e = launch(k_qk_fullnorm_append<__half>, dim3(T), dim3(256), 0, stream, pdl != 0, proj, ldp, q_off, k_off, nq, nk, q_weight,
+        e = launch(k_qk_fullnorm_append<__half>, dim3(T, 2), dim3(512), 0, stream, pdl != 0, proj, ldp, q_off, k_off, nq, nk, q_weight,
                    k_weight, eps, (__half*)q_out, k_addrs, v_addrs, slot, pos);
     ZL_CHECK_CUDA(e);
     return ZL_OK;
@@ -300,16 +373,17 @@ extern "C" int zl_token_shift_mix(const float* x, long long ldx, const float* mu
     ZL_CHECK_ARG(x && mu && state_addrs && slot && pos && out && n_mix > 0 && T > 0 && D > 0 && ldx >= D);
     ZL_CHECK_ARG(out_stride >= (long long)T * D);
     ZL_CHECK_ARG(out_dtype == ZL_F16 || out_dtype == ZL_BF16 || out_dtype == ZL_F32);
+    // 4 channels per thread when every row (x, the stored tokens, mu, out) starts on a 16-byte boundary
+    const bool v4 = D % 4 == 0 && ldx % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(mu)) & 15) == 0;
+    const dim3 grid(T, cdiv(D, 256 * (v4 ? 4 : 1))), block(256);
     cudaError_t e;
-    if (out_dtype == ZL_F32)
-        e = launch(k_token_shift_mix<float>, dim3(T), dim3(256), 0, stream, pdl != 0, x, ldx, mu, n_mix, state_addrs, slot, pos,
-                   (float*)out, out_stride, D, store_state);
-    else if (out_dtype == ZL_BF16)
-        e = launch(k_token_shift_mix<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, pdl != 0, x, ldx, mu, n_mix, state_addrs, slot,
-                   pos, (__nv_bfloat16*)out, out_stride, D, store_state);
-    else
-        e = launch(k_token_shift_mix<__half>, dim3(T), dim3(256), 0, stream, pdl != 0, x, ldx, mu, n_mix, state_addrs, slot, pos,
-                   (__half*)out, out_stride, D, store_state);
+#define ZL_TSM(TO, V)                                                                                                       \
+    launch(k_token_shift_mix<TO, V>, grid, block, 0, stream, pdl != 0, x, ldx, mu, n_mix, state_addrs, slot, pos, (TO*)out, \
+           out_stride, D, store_state)
+    if (out_dtype == ZL_F32) e = v4 ? ZL_TSM(float, 4) : ZL_TSM(float, 1);
+    else if (out_dtype == ZL_BF16) e = v4 ? ZL_TSM(__nv_bfloat16, 4) : ZL_TSM(__nv_bfloat16, 1);
+    else e = v4 ? ZL_TSM(__half, 4) : ZL_TSM(__half, 1);
+#undef ZL_TSM
     ZL_CHECK_CUDA(e);
     return ZL_OK;
 }
@@ -319,15 +393,18 @@ extern "C" int zl_postnorm_combine(float* x, long long ldx, float alpha, const f
                                    int T, int D, float eps, int pdl, zl_stream_t stream) {
     ZL_CHECK_ARG(x && a && weight && T > 0 && D > 0 && ldx >= D && lda >= D && (!b || ldb >= D));
     ZL_CHECK_ARG(!x_act || act_dtype == ZL_F16 || act_dtype == ZL_BF16);
-    ZL_CHECK_SUPPORTED((size_t)D * 4 <= 48 * 1024);
+    const int vec = D % 4 == 0 && D <= 4096 && ldx % 4 == 0 && lda % 4 == 0 && (!b || ldb % 4 == 0) &&
+                    ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) |
+                      reinterpret_cast<uintptr_t>(weight)) & 15) == 0;
+    ZL_CHECK_SUPPORTED(vec || (size_t)D * 4 <= 48 * 1024);
     cudaError_t e;
-    const size_t smem = (size_t)D * 4;
+    const size_t smem = vec ? 0 : (size_t)D * 4;
     if (x_act && act_dtype == ZL_F16)
         e = launch(k_postnorm_combine<__half>, dim3(T), dim3(256), smem, stream, pdl != 0, x, ldx, alpha, a, lda, coef_a, b, ldb,
-                   coef_b, weight, (__half*)x_act, D, eps);
+                   coef_b, weight, (__half*)x_act, D, eps, vec);
     else
         e = launch(k_postnorm_combine<__nv_bfloat16>, dim3(T), dim3(256), smem, stream, pdl != 0, x, ldx, alpha, a, lda, coef_a, b,
-                   ldb, coef_b, weight, (__nv_bfloat16*)x_act, D, eps);
+                   ldb, coef_b, weight, (__nv_bfloat16*)x_act, D, eps, vec);
     ZL_CHECK_CUDA(e);
     return ZL_OK;
 }
