@@ -587,9 +587,9 @@ static int gemm_dispatch(GemmP p, int batch, int in_dtype, int out_dtype, int ep
             e = out_dtype == ZL_F32 ? launch_grouped_small<__half, float>(p, 1, true, pdl != 0, stream)
                                     : launch_grouped_small<__half, __half>(p, 1, true, pdl != 0, stream);
     } else if (!grouped && (epilogue == ZL_GEMM_EPI_TANH || epilogue == ZL_GEMM_EPI_GELU_TANH_MUL) && batch == 1 &&
-               (M <= 8 || (M <= 32 && N <= 512)) && vx && vw && K % 8 == 0 && (size_t)8 * K * 2 <= 160 * 1024) {
-        // a narrow tanh / gelu-times-multiplier projection of a decode step: one column per warp, loads in flight (a tile
-        // kernel would put a handful of CTAs on it)
+               M <= 8 && vx && vw && K % 8 == 0 && (size_t)8 * K * 2 <= 160 * 1024) {
+        // a narrow tanh / gelu-times-multiplier projection of a decode step: one column per warp, loads in flight.  (With more
+        // than 8 rows the kernel re-streams the weights per 8 rows and measured slower than the tile kernel.)
         p.act_tanh = epilogue == ZL_GEMM_EPI_TANH;
         p.act_gelu_mul = epilogue == ZL_GEMM_EPI_GELU_TANH_MUL;
         if (in_dtype == ZL_BF16)
