@@ -193,9 +193,12 @@ int zl_w8a8_gemm(const void* xq, const float* x_scale, const void* w, const void
  * out_dtype f16/bf16/f32. */
 int zl_dense_gemm_skinny(const void* x, int ldx, const void* w, const void* bias, void* y, int M, int N, int K,
                          int dtype, int out_dtype, int pdl, zl_stream_t stream);
-/* the same with an activation on the output: act 0 none, 1 relu(v)^2 */
+/* the same with an activation on the output: act 0 none, 1 relu(v)^2, 2 tanh(v) */
 int zl_dense_gemm_skinny_act(const void* x, int ldx, const void* w, const void* bias, void* y, int M, int N, int K, int dtype,
                              int out_dtype, int act, int pdl, zl_stream_t stream);
+/* act 0 none, 1 relu(v)^2, 2 tanh(v), 3 gelu_tanh(v) * mul[m * ld_mul + n] (mul fp32, device) */
+int zl_dense_gemm_skinny_mul(const void* x, int ldx, const void* w, const void* bias, void* y, int M, int N, int K, int dtype,
+                             int out_dtype, int act, const float* mul, int ld_mul, int pdl, zl_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------ *
  * Norm / residual / activation

@@ -43,8 +43,10 @@ CFG_MIXED = top(67, 48, 512, 6, 1e-5, 1.7, 12.0,
 CFG_ONES = top(40, 32, 400, 1, 1e-6, 1.0, 50.0,
                [D(1, 1, 32, 32, 1, ff=16), P(1, 1, 32, 3, 2, 5.0, 1.0, 1, 32, 1, 1.0, 1.0), P(1, 1, 16, 0, 4, 9.0, 0.25, 1, 8, 2, 1.0, 1.0)])
 CFG_WIDE = top(96, 64, 600, 8, 1e-5, 2.0, 20.0,
-               [P(8, 2, 32, 128, 16, 100.0, 0.18, 2, 64, 8, 0.9, 0.6, ff=96), D(4, 1, 64, 32, 3),
+               [P(8, 2, 32, 300, 16, 100.0, 0.18, 2, 64, 8, 0.9, 0.6, ff=96), D(4, 1, 64, 32, 3),
                 P(8, 4, 16, 100, 12, 80.0, 0.25, 4, 16, 4, 0.5, 1.0, ff=48)])
+# decay path and side input at least 64 wide: steps of 9 .. 32 rows take them through the skinny kernel's activations
+CFG_BATCH = top(50, 64, 256, 64, 1e-5, 1.5, 15.0, [P(4, 2, 16, 50, 8, 40.0, 0.2, 2, 32, 64, 0.8, 0.7, ff=64), D(2, 1, 32, 32, 2)])
 CONFIGS = {"mixed": CFG_MIXED, "ones": CFG_ONES, "wide": CFG_WIDE}
 
 
@@ -137,6 +139,25 @@ def test_gemm_gated_pair_multiplier_and_cap_epilogues(cuda, lib, dtype, rows):
     got = ops.gemm_nt_fused(dev(x, cuda, td), dev(wu * 4, cuda, td), None, torch.float32, ops.GEMM_EPI_SOFTCAP, limit=2.5)
     want = 2.5 * np.tanh(xd @ (wu.T * 4.0) / 2.5)
     assert np.abs(want).max() > 2.4 and np.abs(got.cpu().numpy() - want).max() < tol * 2.5
+
+
+def test_skinny_linear_activations(cuda, lib):
+    """tanh and gelu_tanh(v) * multiplier on the output of the skinny Linear, 20 and 45 rows (two passes of the kernel)."""
+    import torch
+    from zhilight_b200 import ops
+    rng = np.random.default_rng(9)
+    for rows in (20, 45):
+        K, N = 96, 72
+        x = orc.bf16_round(rng.standard_normal((rows, K)).astype(np.float32))
+        w = orc.bf16_round(rng.standard_normal((N, K)).astype(np.float32) / 4)
+        mul = rng.standard_normal((rows, N + 5)).astype(np.float32)
+        z = x.astype(np.float64) @ w.T
+        got = ops.dense_gemm_skinny_mul(dev(x, cuda, torch.bfloat16), dev(w, cuda, torch.bfloat16), 2, out_dtype=torch.float32)
+        assert np.abs(got.cpu().numpy() - np.tanh(z)).max() < 1e-4
+        got = ops.dense_gemm_skinny_mul(dev(x, cuda, torch.bfloat16), dev(w, cuda, torch.bfloat16), 3, mul=dev(mul, cuda),
+                                        out_dtype=torch.float32)
+        want = orc.gelu_tanh(z) * mul[:, :N]
+        assert np.abs(got.cpu().numpy() - want).max() < 1e-4 * max(1.0, np.abs(want).max())
 
 
 def test_distance_table_rows(lib):
@@ -549,9 +570,35 @@ def test_unequal_batch_against_each_alone_and_slot_reuse(cuda, lib, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_twenty_requests_decode_together(cuda, lib, dtype):
+    """20 requests with prompts of 1 .. 20 tokens, then 12 steps in which all decode together (steps of 20 rows take the
+    narrow projections through other kernels than steps of up to 8 rows); every row against the request alone."""
+    from zhilight_b200.engine import Engine
+    cfg, W, m = make(CFG_BATCH, dtype, seed=7, max_batch=20, max_seq=64, max_step_tokens=64)
+    eng = Engine(m)
+    seqs = [tokens_for(CFG_BATCH, 13 + i, 40 + i) for i in range(20)]
+    want = [orc.forward(CFG_BATCH, W, t)[0] for t in seqs]
+    got = [[] for _ in seqs]
+    for i in range(20):
+        eng.open(i)
+    for lo in (0, 7):        # prompts in two steps of unequal portions
+        res = eng.forward_step([(i, seqs[i][:i + 1], list(range(i + 1))) for i in range(lo, 20 if lo else 7)])
+        for i, r in res.items():
+            got[i].append(r[1])
+    for step in range(12):
+        res = eng.forward_step([(i, [seqs[i][i + 1 + step]], [0]) for i in range(20)])
+        for i, r in res.items():
+            got[i].append(r[1])
+    for i in range(20):
+        assert rel_err(np.concatenate(got[i]), want[i]) < TOL[dtype], (dtype, i)
+    m.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_through_graphs_blocks_and_splits(cuda, lib, dtype):
     """A short prompt and then 330 single-token steps: the decode graph, the length buckets and the key splits change on
-    the way, block edges (100, 128, 200, 256, 300) are crossed token by token, the states are carried through 340 updates."""
+    the way (blocks of 300 keys are cut in two splits once the length bucket allows it), block edges (100, 200, 300) are
+    crossed token by token, the states are carried through 340 updates."""
     cfg, W, m = make(CFG_WIDE, dtype, seed=4, max_batch=2, max_seq=512, max_step_tokens=16)
     toks = tokens_for(cfg.to_dict(), 340, 11)
     want = orc.forward(CFG_WIDE, W, toks)[0]
@@ -566,13 +613,13 @@ def test_long_decoding_through_graphs_blocks_and_splits(cuda, lib, dtype):
 
 def test_far_and_edge_tokens_are_found_through_the_model(cuda, lib):
     """With decays next to one, changing token 7 of 300 moves the last logits by far more than the float32 tolerance
-    (through the recurrent states), and so does the first token of the last block (through attention as well): the oracle
+    (through the recurrent states), and so does the first token of the last layer's last block (through attention as well): the oracle
     says so first, then the framework must follow both through prompt portions and decoding."""
     cfg, W, m = make(CFG_WIDE, "float32", seed=5, max_batch=2, max_seq=320, max_step_tokens=64, long_memory=True)
     toks = tokens_for(cfg.to_dict(), 300, 13)
     base = orc.forward(CFG_WIDE, W, toks)[0][-1]
     cases = [(toks, base)]
-    for where in (7, 256):
+    for where in (7, 200):
         other = list(toks)
         other[where] = (toks[where] + 1) % cfg.vocab
         moved = orc.forward(CFG_WIDE, W, other)[0][-1]

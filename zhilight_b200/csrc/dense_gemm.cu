@@ -36,7 +36,7 @@ __device__ __forceinline__ void mma_t<__nv_bfloat16>(float (&d)[4], const uint32
 template <typename T, typename TO, int NT, int KS, int UNROLL>
 __global__ void __launch_bounds__(kDenseWarps * 32, 2)
 k_dense_skinny(const T* __restrict__ x, int ldx, const T* __restrict__ w, const T* __restrict__ bias,
-               TO* __restrict__ y, int mc, int N, int K, unsigned long long* trace, int act) {
+               TO* __restrict__ y, int mc, int N, int K, unsigned long long* trace, int act, const float* mul, int ld_mul) {
     constexpr int TPC = kDenseWarps / KS;   // tiles per CTA per pass
     __shared__ float red[KS > 1 ? kDenseWarps : 1][NT][4][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -149,6 +149,10 @@ k_dense_skinny(const T* __restrict__ x, int ldx, const T* __restrict__ w, const 
                         if (act == 1) {   // relu^2
                             v = fmaxf(v, 0.f);
                             v *= v;
+                        } else if (act == 2) {
+                            v = tanhf(v);
+                        } else if (act == 3) {   // the tanh form of gelu, times a multiplier per (token, column)
+                            v = gelu_f(v) * mul[(size_t)tok * ld_mul + row];
                         }
                         y[(size_t)tok * N + row] = from_f32<TO>(v);
                     }
@@ -168,7 +172,7 @@ k_dense_skinny(const T* __restrict__ x, int ldx, const T* __restrict__ w, const 
 
 template <typename T, typename TO, int NT>
 static cudaError_t launch_dense_ks(const T* x, int ldx, const T* w, const T* bias, TO* y, int mc, int N, int K,
-                                   bool pdl, cudaStream_t stream, int act) {
+                                   bool pdl, cudaStream_t stream, int act, const float* mul, int ld_mul) {
     const int tiles = cdiv(N, 16);
     static int sms = 0;
     if (sms == 0) {
@@ -191,7 +195,7 @@ static cudaError_t launch_dense_ks(const T* x, int ldx, const T* w, const T* bia
         const int groups = cdiv(tiles, kDenseWarps / KS_);                                                             \
         const int grid = groups < sms * 2 ? groups : sms * 2;                                                          \
         return launch(k_dense_skinny<T, TO, NT, KS_, UNROLL>, dim3(grid), block, 0, stream, pdl, x, ldx, w, bias, y, mc, \
-                      N, K, g_w4_trace, act);                                                                          \
+                      N, K, g_w4_trace, act, mul, ld_mul);                                                                          \
     }
     if (ks == 1) ZL_DENSE_LAUNCH(1);
     if (ks == 2) ZL_DENSE_LAUNCH(2);
@@ -202,18 +206,18 @@ static cudaError_t launch_dense_ks(const T* x, int ldx, const T* w, const T* bia
 
 template <typename T, typename TO>
 static cudaError_t launch_dense(const T* x, int ldx, const T* w, const T* bias, TO* y, int mc, int N, int K,
-                                bool pdl, cudaStream_t stream, int act) {
-    if (mc <= 8) return launch_dense_ks<T, TO, 1>(x, ldx, w, bias, y, mc, N, K, pdl, stream, act);
-    if (mc <= 16) return launch_dense_ks<T, TO, 2>(x, ldx, w, bias, y, mc, N, K, pdl, stream, act);
-    return launch_dense_ks<T, TO, 4>(x, ldx, w, bias, y, mc, N, K, pdl, stream, act);
+                                bool pdl, cudaStream_t stream, int act, const float* mul, int ld_mul) {
+    if (mc <= 8) return launch_dense_ks<T, TO, 1>(x, ldx, w, bias, y, mc, N, K, pdl, stream, act, mul, ld_mul);
+    if (mc <= 16) return launch_dense_ks<T, TO, 2>(x, ldx, w, bias, y, mc, N, K, pdl, stream, act, mul, ld_mul);
+    return launch_dense_ks<T, TO, 4>(x, ldx, w, bias, y, mc, N, K, pdl, stream, act, mul, ld_mul);
 }
 
 template <typename T>
 static cudaError_t dispatch_out(const T* x, int ldx, const T* w, const T* bias, void* y, int mc, int N, int K,
-                                int out_dtype, bool pdl, cudaStream_t stream, size_t y_off, int act) {
+                                int out_dtype, bool pdl, cudaStream_t stream, size_t y_off, int act, const float* mul, int ld_mul) {
     if (out_dtype == ZL_F32)
-        return launch_dense<T, float>(x, ldx, w, bias, static_cast<float*>(y) + y_off, mc, N, K, pdl, stream, act);
-    return launch_dense<T, T>(x, ldx, w, bias, static_cast<T*>(y) + y_off, mc, N, K, pdl, stream, act);
+        return launch_dense<T, float>(x, ldx, w, bias, static_cast<float*>(y) + y_off, mc, N, K, pdl, stream, act, mul, ld_mul);
+    return launch_dense<T, T>(x, ldx, w, bias, static_cast<T*>(y) + y_off, mc, N, K, pdl, stream, act, mul, ld_mul);
 }
 
 }  // namespace zl
@@ -227,7 +231,15 @@ extern "C" int zl_dense_gemm_skinny(const void* x, int ldx, const void* w, const
 
 extern "C" int zl_dense_gemm_skinny_act(const void* x, int ldx, const void* w, const void* bias, void* y, int M, int N,
                                         int K, int dtype, int out_dtype, int act, int pdl, zl_stream_t stream) {
-    ZL_CHECK_ARG(x && w && y && M > 0 && N > 0 && K > 0 && (act == 0 || act == 1));
+    ZL_CHECK_ARG(act == 0 || act == 1 || act == 2);
+    return zl_dense_gemm_skinny_mul(x, ldx, w, bias, y, M, N, K, dtype, out_dtype, act, nullptr, 0, pdl, stream);
+}
+
+extern "C" int zl_dense_gemm_skinny_mul(const void* x, int ldx, const void* w, const void* bias, void* y, int M, int N,
+                                        int K, int dtype, int out_dtype, int act, const float* mul_all, int ld_mul, int pdl,
+                                        zl_stream_t stream) {
+    ZL_CHECK_ARG(x && w && y && M > 0 && N > 0 && K > 0 && act >= 0 && act <= 3);
+    ZL_CHECK_ARG(act != 3 || (mul_all && ld_mul >= N));
     ZL_CHECK_ARG(dtype == ZL_F16 || dtype == ZL_BF16);
     ZL_CHECK_ARG(out_dtype == dtype || out_dtype == ZL_F32);
     ZL_CHECK_SUPPORTED(K % 32 == 0);
@@ -238,16 +250,17 @@ extern "C" int zl_dense_gemm_skinny_act(const void* x, int ldx, const void* w, c
     for (int m0 = 0; m0 < M; m0 += 32) {
         const int mc = (M - m0) < 32 ? (M - m0) : 32;
         const bool use_pdl = pdl != 0 && m0 == 0;
+        const float* mul = mul_all ? mul_all + (size_t)m0 * ld_mul : nullptr;
         cudaError_t e;
         if (dtype == ZL_F16)
             e = dispatch_out<__half>(static_cast<const __half*>(x) + (size_t)m0 * ldx, ldx,
                                      static_cast<const __half*>(w), static_cast<const __half*>(bias), y, mc, N,
-                                     K, out_dtype, use_pdl, stream, (size_t)m0 * N, act);
+                                     K, out_dtype, use_pdl, stream, (size_t)m0 * N, act, mul, ld_mul);
         else
             e = dispatch_out<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(x) + (size_t)m0 * ldx, ldx,
                                             static_cast<const __nv_bfloat16*>(w),
                                             static_cast<const __nv_bfloat16*>(bias), y, mc, N, K, out_dtype,
-                                            use_pdl, stream, (size_t)m0 * N, act);
+                                            use_pdl, stream, (size_t)m0 * N, act, mul, ld_mul);
         ZL_CHECK_CUDA(e);
     }
     return ZL_OK;

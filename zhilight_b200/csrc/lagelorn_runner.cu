@@ -385,9 +385,13 @@ int linear(zl_lagelorn* m, const void* x, int K, const void* w, int N, const flo
            int M, int out_dtype, int epi) {
     const auto& c = m->cfg;
     static const bool no_skinny = getenv("ZL_LAGELORN_NO_SKINNY") != nullptr;
-    if (!no_skinny && c.dtype != ZL_F32 && epi == ZL_GEMM_EPI_NONE && M <= 32 && K % 32 == 0 && N >= 64 && (!bias_f32 || bias_act) &&
+    // the skinny kernel: plain Linears of up to 32 rows, and the narrow tanh projection of 9 .. 32 rows (a tile kernel would
+    // put one CTA on its 64 columns; up to 8 rows the streamed few-rows kernel inside zl_gemm_nt_bias is the faster one)
+    const bool skinny_epi = epi == ZL_GEMM_EPI_NONE || (epi == ZL_GEMM_EPI_TANH && M > 8);
+    if (!no_skinny && c.dtype != ZL_F32 && skinny_epi && M <= 32 && K % 32 == 0 && N >= 64 && (!bias_f32 || bias_act) &&
         (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0)
-        return zl_dense_gemm_skinny_act(x, K, w, bias_act, y, M, N, K, c.dtype, out_dtype, 0, pdl_for(m, 1, M), m->stream);
+        return zl_dense_gemm_skinny_act(x, K, w, bias_act, y, M, N, K, c.dtype, out_dtype, epi == ZL_GEMM_EPI_TANH ? 2 : 0,
+                                        pdl_for(m, 1, M), m->stream);
     return zl_gemm_nt_bias(x, K, w, K, bias_f32, y, N, M, N, K, c.dtype, out_dtype, epi, pdl_for(m, 2, M), m->stream);
 }
 
@@ -465,8 +469,12 @@ int enqueue_step(zl_lagelorn* m, int T, int n_want, int n_runs, int max_run, int
                                        st));
         }
         // the layer's slice of the token's second embedding
-        RCHECK(zl_gemm_nt_fused(xin, D, L.s_gate, D, nullptr, m->sg, c.side_dim, T, c.side_dim, D, dt, dt, ZL_GEMM_EPI_GELU_TANH_MUL,
-                                m->side + (size_t)l * c.side_dim, S, 0.f, pg, st));
+        if (dt != ZL_F32 && T > 8 && T <= 32 && D % 32 == 0 && c.side_dim >= 64 && (reinterpret_cast<uintptr_t>(L.s_gate) & 15) == 0)
+            RCHECK(zl_dense_gemm_skinny_mul(xin, D, L.s_gate, nullptr, m->sg, T, c.side_dim, D, dt, dt, 3,
+                                            m->side + (size_t)l * c.side_dim, S, pdl_for(m, 1, T), st));
+        else
+            RCHECK(zl_gemm_nt_fused(xin, D, L.s_gate, D, nullptr, m->sg, c.side_dim, T, c.side_dim, D, dt, dt,
+                                    ZL_GEMM_EPI_GELU_TANH_MUL, m->side + (size_t)l * c.side_dim, S, 0.f, pg, st));
         RCHECK(linear(m, m->sg, c.side_dim, L.s_proj, D, nullptr, nullptr, m->y, T, ZL_F32, ZL_GEMM_EPI_NONE));
         RCHECK(zl_rmsnorm_residual_combine(m->y, D, nullptr, 1, L.s_norm, m->x, D, xa_out, dt, T, D, c.eps, pr, st));
         if (m->capture && m->layer_dump)

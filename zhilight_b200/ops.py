@@ -607,6 +607,16 @@ def gemm_nt_fused(x, w, bias=None, out_dtype=None, epilogue=GEMM_EPI_NONE, mul=N
     return y
 
 
+def dense_gemm_skinny_mul(x, w, act, mul=None, out_dtype=None):
+    """Skinny Linear with an activation on the output: act 0 none, 1 relu^2, 2 tanh, 3 gelu_tanh(v) * mul[m, n] (mul fp32)."""
+    m, k = x.shape
+    n = w.shape[0]
+    y = torch.empty((m, n), dtype=out_dtype or x.dtype, device=x.device)
+    _lib.call("zl_dense_gemm_skinny_mul", _p(x), k, _p(w), None, _p(y), m, n, k, _dt(x), _dt(y), act, _p(mul),
+              mul.shape[1] if mul is not None else 0, 0, _stream())
+    return y
+
+
 def distance_bias_table(table, far, n_dist):
     """table (rows, heads) numpy float32 -> (heads, n_dist) numpy float32: the table's row for every distance below n_dist."""
     import numpy as np
