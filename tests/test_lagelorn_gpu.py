@@ -360,7 +360,7 @@ def test_norm_after_the_sum(cuda, lib):
         assert np.abs(xd.cpu().numpy() - orc.rms_norm(x.astype(np.float64) + a, w, 1e-5)).max() < 1e-5
 
 
-@pytest.mark.parametrize("shape", [(4, 2, 32, 24, 4), (3, 3, 24, 20, 2), (2, 1, 64, 32, 1), (2, 2, 16, 40, 3)])
+@pytest.mark.parametrize("shape", [(4, 2, 32, 24, 4), (3, 3, 24, 20, 2), (2, 1, 64, 32, 1), (2, 2, 16, 40, 3), (2, 1, 128, 48, 2)])
 def test_gated_delta_rule_runs_portions_and_slot_reuse(cuda, lib, shape):
     """Three sequences fed through a plan of mixed steps; convolution inputs cross the step borders through the rings, the
     states through the slots.  One token's keys are made tiny (the constant under the root of the unit norm shows).  Then
@@ -421,7 +421,7 @@ def _delta_inputs(pr, conv, a_log, dt_bias, H, G, dk, dv):
             np.exp(-np.exp(a_log.astype(np.float64)) * orc.softplus(p64[:, 3 + C + H:] + dt_bias)))
 
 
-@pytest.mark.parametrize("dk", [32, 24, 64])
+@pytest.mark.parametrize("dk", [32, 24, 64, 128])
 def test_decaying_state_with_bonus_runs_and_slot_reuse(cuda, lib, dk):
     import torch
     from zhilight_b200 import ops

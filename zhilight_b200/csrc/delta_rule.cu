@@ -4,15 +4,16 @@
 // rate a_t = sigmoid(rate_logit_t) per key channel; both subtracted terms read S_(t-1).
 //
 // The columns of S (one per value channel) never meet: S_t[:, j] depends on S_(t-1)[:, j] and on the token's vectors
-// only.  A thread owns one column and walks the tokens of its sequence in order, so the result of a token does not
-// depend on how the sequence was cut into steps or on the other sequences of the step.  A CTA owns `cols` columns of
-// one head of one run (the consecutive rows of one slot in the step).  The token vectors (u, a*u, w, k, r, v) are
-// prepared for all tokens at once by a kernel of their own; the recurrence stages them chunk by chunk in shared
-// memory ahead of use.  The column lives in registers when dk is one of the compiled sizes, in shared memory otherwise.
+// only.  A column is walked through the tokens of its sequence in order, so the result of a token does not depend on
+// how the sequence was cut into steps or on the other sequences of the step.  A CTA owns 32 columns of one head of one
+// run (the consecutive rows of one slot in the step).  The token vectors (u, a*u, w, k, r, v) are prepared for all
+// tokens at once by a kernel of their own; the recurrence stages them chunk by chunk in shared memory ahead of use.
+// For the compiled key sizes (32, 64, 128) a column lives in the registers of four adjacent lanes (k_delta_rule_quad;
+// ZL_DELTA_NO_QUAD: of one thread, k_delta_rule), for other sizes in shared memory, one thread per column.
 // A run that starts at position 0 starts from a zero state (a slot given to a new sequence needs no clearing); the
 // final state goes back to the slot.  Everything is fp32.
 //
-// Two more recurrences run on the same column kernel, each with a preparation kernel of its own that writes the same
+// Two more recurrences run on the same column kernels, each with a preparation kernel of its own that writes the same
 // six token vectors:
 //   * gated delta rule:  S <- g S;  e = beta (v - S^T k);  S <- S + k e^T;  o = S^T q, with a scalar decay g and a
 //     scalar rate beta per head and unit q, k.  Expanded, S_t = g S_(t-1) - (g beta k)(k^T S_(t-1)) + (beta k) v^T: the
@@ -221,6 +222,118 @@ static int launch_delta(const DeltaP& p, int runs, int block, bool pdl, cudaStre
     return ZL_OK;
 }
 
+// The same recurrence with a column of S spread over LANES adjacent lanes: a lane holds DK / LANES entries of its column in
+// registers -- the 4-element pieces f = LANES i + q of the key dimension, so that the lanes' 16-byte reads of a staged
+// vector fall into different banks -- and the dot products are finished with log2(LANES) shuffles.  A head then occupies
+// LANES warps per 32 columns instead of one: a prompt of one sequence runs on heads * dv / 32 CTAs only, each token is a
+// dependent chain, and one warp per scheduler issues an instruction every 4 - 5 cycles; more warps with fewer instructions
+// each is what shortens it.  The sums are taken in an order fixed by the token (piece by piece, then over the lanes),
+// whatever the step.  grid (dv / 32 rounded up, H, runs); block 32 * LANES.
+template <int DK, int LANES, bool READ_FIRST>
+__global__ void __launch_bounds__(32 * LANES) k_delta_rule_quad(DeltaP p) {
+    extern __shared__ __align__(16) float dsm[];
+    constexpr int Q = DK / LANES, NT = 32 * LANES;      // entries per lane (a multiple of 4), threads
+    static_assert(Q % 4 == 0 && Q >= 4, "a lane holds whole 4-element pieces");
+    const int per = 5 * DK + p.dv;
+    float* tok = dsm;                                   // [2][chunk][per]
+    pdl_trigger();
+    pdl_wait();
+    const int run = blockIdx.z, h = blockIdx.y, tid = threadIdx.x;
+    const int row0 = p.run_row0[run], len = p.run_len[run];
+    if (len <= 0) return;
+    const int q = tid % LANES, col = tid / LANES;       // my share of the keys, my column inside the CTA
+    const int j = blockIdx.x * 32 + col;                // my value channel
+    const bool mine = j < p.dv;                         // the lanes of a column agree
+    float* sg = static_cast<float*>(p.state_addrs[p.slot[row0]]) + (size_t)h * DK * p.dv;
+    const bool fresh = p.pos[row0] == 0;
+    auto stage = [&](int buf, int c0) {
+        const int cn = min(p.chunk, len - c0);
+        float* dst = tok + (size_t)buf * p.chunk * per;
+        const float* src = p.prep + ((size_t)(row0 + c0) * p.H + h) * per;
+        for (int tt = 0; tt < cn; ++tt, dst += per, src += (size_t)p.H * per)
+            for (int i = tid * 4; i < per; i += NT * 4) dr_cp_async16(dst + i, src + i);
+    };
+    stage(0, 0);
+    dr_cp_commit();
+    // S[4 i + c] is key (LANES i + q) * 4 + c of my column
+    float S[Q];
+#pragma unroll
+    for (int m = 0; m < Q; ++m) S[m] = (fresh || !mine) ? 0.f : sg[(size_t)((LANES * (m >> 2) + q) * 4 + (m & 3)) * p.dv + j];
+    float* optr = p.o + (size_t)row0 * p.ld_o + (size_t)h * p.dv + j;
+    const int vcol = 5 * DK + (mine ? j : 0);
+    int buf = 0;
+    for (int c0 = 0; c0 < len; c0 += p.chunk, buf ^= 1) {
+        const int cn = min(p.chunk, len - c0);
+        dr_cp_wait_all();
+        __syncthreads();   // this chunk has landed for every thread; the other half is no longer read
+        if (c0 + p.chunk < len) stage(buf ^ 1, c0 + p.chunk);
+        dr_cp_commit();
+        const float* tv = tok + (size_t)buf * p.chunk * per;
+        for (int tt = 0; tt < cn; ++tt, tv += per, optr += p.ld_o) {
+            const float vj = mine ? tv[vcol] : 0.f;
+            const float4* mq = reinterpret_cast<const float4*>(tv) + q;   // piece i of a vector at DK/4 * vector + LANES * i
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll
+            for (int i = 0; i < Q / 4; ++i) {
+                const float4 u = mq[LANES * i];
+                d0 = fmaf(u.x, S[4 * i], d0), d1 = fmaf(u.y, S[4 * i + 1], d1), d2 = fmaf(u.z, S[4 * i + 2], d2), d3 = fmaf(u.w, S[4 * i + 3], d3);
+            }
+            float dot = (d0 + d1) + (d2 + d3);
+#pragma unroll
+            for (int x = 1; x < LANES; x <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, x);
+            float out;
+            if constexpr (READ_FIRST) {
+#pragma unroll
+                for (int i = 0; i < Q / 4; ++i) {
+                    const float4 w = mq[2 * (DK / 4) + LANES * i];
+                    const float4 kk = mq[3 * (DK / 4) + LANES * i];
+                    S[4 * i] = fmaf(kk.x, vj, w.x * S[4 * i]);
+                    S[4 * i + 1] = fmaf(kk.y, vj, w.y * S[4 * i + 1]);
+                    S[4 * i + 2] = fmaf(kk.z, vj, w.z * S[4 * i + 2]);
+                    S[4 * i + 3] = fmaf(kk.w, vj, w.w * S[4 * i + 3]);
+                }
+                out = fmaf(tv[4 * DK], vj, dot);
+            } else {
+                float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < Q / 4; ++i) {
+                    const float4 au = mq[(DK / 4) + LANES * i];
+                    const float4 w = mq[2 * (DK / 4) + LANES * i];
+                    const float4 kk = mq[3 * (DK / 4) + LANES * i];
+                    const float4 rr = mq[4 * (DK / 4) + LANES * i];
+                    S[4 * i] = fmaf(kk.x, vj, fmaf(-au.x, dot, w.x * S[4 * i]));
+                    S[4 * i + 1] = fmaf(kk.y, vj, fmaf(-au.y, dot, w.y * S[4 * i + 1]));
+                    S[4 * i + 2] = fmaf(kk.z, vj, fmaf(-au.z, dot, w.z * S[4 * i + 2]));
+                    S[4 * i + 3] = fmaf(kk.w, vj, fmaf(-au.w, dot, w.w * S[4 * i + 3]));
+                    o0 = fmaf(S[4 * i], rr.x, o0), o1 = fmaf(S[4 * i + 1], rr.y, o1), o2 = fmaf(S[4 * i + 2], rr.z, o2), o3 = fmaf(S[4 * i + 3], rr.w, o3);
+                }
+                out = (o0 + o1) + (o2 + o3);
+#pragma unroll
+                for (int x = 1; x < LANES; x <<= 1) out += __shfl_xor_sync(0xffffffffu, out, x);
+            }
+            if (mine && q == 0) *optr = out;
+        }
+    }
+    if (mine) {
+#pragma unroll
+        for (int m = 0; m < Q; ++m) sg[(size_t)((LANES * (m >> 2) + q) * 4 + (m & 3)) * p.dv + j] = S[m];
+    }
+}
+
+template <int DK, int LANES, bool READ_FIRST>
+static int launch_delta_quad(const DeltaP& p, int runs, bool pdl, cudaStream_t st) {
+    const size_t smem = delta_smem(DK, p.dk, p.dv, 32 * LANES);
+    if (smem > 48 * 1024) {
+        static size_t set_for = 0;
+        if (smem > set_for) {
+            ZL_CHECK_CUDA(cudaFuncSetAttribute(k_delta_rule_quad<DK, LANES, READ_FIRST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            set_for = smem;
+        }
+    }
+    ZL_CHECK_CUDA(launch(k_delta_rule_quad<DK, LANES, READ_FIRST>, dim3(cdiv(p.dv, 32), p.H, runs), dim3(32 * LANES), smem, st, pdl, p));
+    return ZL_OK;
+}
+
 // the column kernel over prepared token vectors: registers for the compiled key sizes, shared memory otherwise
 template <bool READ_FIRST>
 static int run_columns(DeltaP& p, int runs, bool pdl, cudaStream_t st) {
@@ -228,7 +341,20 @@ static int run_columns(DeltaP& p, int runs, bool pdl, cudaStream_t st) {
     p.cols = 32;
     const int block = 32;
     static const bool no_reg_env = getenv("ZL_DELTA_NO_REG") != nullptr;
+    static const bool no_quad = getenv("ZL_DELTA_NO_QUAD") != nullptr;
     const bool no_reg = no_reg_env || (5 * p.dk + p.dv) % 4 != 0;   // the register kernel reads the staged vectors 16 bytes at a time
+    static const int lanes_env = getenv("ZL_DELTA_LANES") ? atoi(getenv("ZL_DELTA_LANES")) : 4;
+    if (!no_reg && !no_quad) {   // a column over 4 or 8 adjacent lanes
+        if (lanes_env == 4) {
+            if (p.dk == 32) return launch_delta_quad<32, 4, READ_FIRST>(p, runs, pdl, st);
+            if (p.dk == 64) return launch_delta_quad<64, 4, READ_FIRST>(p, runs, pdl, st);
+            if (p.dk == 128) return launch_delta_quad<128, 4, READ_FIRST>(p, runs, pdl, st);
+        } else {
+            if (p.dk == 32) return launch_delta_quad<32, 8, READ_FIRST>(p, runs, pdl, st);
+            if (p.dk == 64) return launch_delta_quad<64, 8, READ_FIRST>(p, runs, pdl, st);
+            if (p.dk == 128) return launch_delta_quad<128, 8, READ_FIRST>(p, runs, pdl, st);
+        }
+    }
     if (!no_reg && p.dk == 32) return launch_delta<32, READ_FIRST>(p, runs, block, pdl, st);
     if (!no_reg && p.dk == 64) return launch_delta<64, READ_FIRST>(p, runs, block, pdl, st);
     if (!no_reg && p.dk == 128) return launch_delta<128, READ_FIRST>(p, runs, block, pdl, st);
