@@ -438,11 +438,16 @@ int zl_gemm_nt_fused(const void* x, long long ldx, const void* w, long long ldw,
  * group_offsets[g] .. group_offsets[g+1] (device, groups + 1 ints) and the weight block w + g * w_group_stride (N, K).
  * List entry i reads row x_rows[i] of x (NULL: row i) and writes row y_rows[i] of y (NULL: row i).  max_rows bounds the
  * rows of any group (the step's row count); the offsets are read on the device, so the call can be captured in a graph.
- * Epilogue none, or the clamped gated unit over column pairs (y has N / 2 columns). */
+ * Epilogue none, relu^2, or the clamped gated unit over column pairs (y has N / 2 columns). */
 int zl_gemm_nt_grouped(const void* x, long long ldx, const int32_t* x_rows, const void* w, long long ldw,
                        long long w_group_stride, void* y, long long ldy, const int32_t* y_rows, const int32_t* group_offsets,
                        int groups, int max_rows, int N, int K, int in_dtype, int out_dtype, int epilogue, float limit,
                        float alpha, float beta, int pdl, zl_stream_t stream);
+/* One problem with the clamped gated unit over column pairs and a per-column fp32 bias (NULL: none; 2 entries per output
+ * column, added before the unit): y (M, N / 2) = g sigmoid(alpha g) (u + beta), g = min(gate, limit), u = clamp(up, +-limit). */
+int zl_gemm_nt_glu_clamp(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* y, long long ldy,
+                         int M, int N, int K, int in_dtype, int out_dtype, float limit, float alpha, float beta, int pdl,
+                         zl_stream_t stream);
 /* y[t] = w * x[t] / sqrt(mean(x[t]^2 over each of `groups` equal consecutive parts) + eps); x fp32, y out_dtype. */
 int zl_group_rmsnorm(const float* x, long long ldx, const float* weight, void* y, long long ldy, int T, int D, int groups,
                      float eps, int out_dtype, int pdl, zl_stream_t stream);
@@ -651,6 +656,49 @@ int zl_moe_route(const float* x, long long ldx, const float* w_router, const flo
                  float* top_weights, int32_t* group_offsets, int32_t* list_token, int32_t* list_pair, int T, int D,
                  int experts, int top, int score_fn, int renormalize, int pdl, zl_stream_t stream);
 
+/* The same from the router's input x (w_router != NULL) or from ready logits (w_router NULL: x is (T, slots) fp32 with row
+ * stride ldx), with restricted choice: the `slots` router outputs form `groups` equal groups of neighbours, a group ranks
+ * by its largest score + correction, and only slots of the `keep` best groups can be chosen (ties: the lower index).  The
+ * weights are the chosen scores, divided by (their sum + renorm_eps) when renormalize != 0.  Slots from `experts` on have
+ * no weights (a caller's identity slots): the lists are sorted over all `slots` groups, group_offsets has slots + 1
+ * entries, and a grouped GEMM over the first `experts` groups skips them. */
+int zl_moe_route_grouped(const float* x, long long ldx, const float* w_router, const float* correction, int32_t* top_experts,
+                         float* top_weights, int32_t* group_offsets, int32_t* list_token, int32_t* list_pair, int T, int D,
+                         int slots, int top, int groups, int keep, int score_fn, int renormalize, float renorm_eps, int pdl,
+                         zl_stream_t stream);
+/* cos / sin of pos[t] * inv_freq[i] (double angles, evaluated in double) -> table (T, half) of float pairs (cos, sin). */
+int zl_rope_table(const int32_t* pos, int T, const double* inv_freq, int half, float* table, int pdl, zl_stream_t stream);
+enum { ZL_ROT_HALVES = 0 /* pair (i, i + n / 2) */, ZL_ROT_ADJACENT = 1 /* pair (2i, 2i + 1) */ };
+/* From a fused projection row proj[t] (fp32) to attention operands with tables of zl_rope_table: the first rot_dims
+ * dimensions of every query head turn by qk_table[t] (rot_dims / 2 pairs in `layout`) -> q_out (T, heads * dim) of `dtype`;
+ * when k_off >= 0 the same for the key heads -> row pos[t] of k_addrs[slot[t]], and every value head -> row pos[t] of
+ * v_addrs[slot[t]], turned over all vdim dimensions by v_table[t] (vdim / 2 pairs) when v_table != NULL. */
+int zl_qkv_table_rope_append(const float* proj, long long ldp, int q_off, int k_off, int v_off, int heads, int kv_heads, int dim,
+                       int vdim, const float* qk_table, int rot_dims, const float* v_table, int layout, void* q_out,
+                       void* const* k_addrs, void* const* v_addrs, const int32_t* slot, const int32_t* pos, int T, int dtype,
+                       int pdl, zl_stream_t stream);
+/* zl_sink_attention_local with two more options.  no_sink != 0: an ordinary softmax (no extra term in the denominator;
+ * `sink` is ignored).  out_table != NULL (a table of zl_rope_table, (T, vdim / 2)): every head's output at token t is
+ * turned back by the table's angles (pair (u, v) -> (u cos + v sin, v cos - u sin), pairs over vdim in out_layout) in
+ * fp32 before it is stored: the inverse of a rotation the cached values carry. */
+int zl_sink_attention_ex(const void* q, void* const* k_addrs, void* const* v_addrs, const int32_t* slot, const int32_t* pos,
+                         const float* sink, int no_sink, const float* gate, long long ldg, float scale, int chunk,
+                         const float* dist_bias, int n_dist, const float* out_table, int out_layout, void* out, int T, int heads,
+                         int kv_heads, int dim, int vdim, int splits, void* workspace, size_t workspace_bytes,
+                         const int32_t* run_row0, const int32_t* run_len, int runs, int max_run_len, int dtype, int pdl,
+                         zl_stream_t stream);
+/* The residual update of a layer whose sublayers read one norm of x and are gated per channel:
+ *   x[t] += mult * (scale_a * sigmoid(gates[t][ga_off + c]) * a[t] + scale_f * sigmoid(gates[t][gf_off + c]) * f[t]),
+ *   f[t] = sum_p coef[t][p] * (choice[t][p] < n_real ? parts[t * n_parts + p] : h[t]) + f_dense[t]
+ * with h[t] = norm_w * x[t] / sqrt(mean(x[t]^2) + eps) of the x before the update (the sublayers' input, recomputed for
+ * choices that hand it through).  a, parts, f_dense fp32 (T or T * n_parts rows of D); parts / f_dense may be NULL (no
+ * such term; both NULL: no second sublayer); choice NULL: every part is real.  next_w != NULL: the next layer's input
+ * next_w * x[t] / sqrt(mean(x[t]^2) + eps) of the new x -> h_next (T, D) of act_dtype. */
+int zl_gated_parallel_combine(float* x, long long ldx, float mult, const float* gates, long long ldg, const float* a,
+                              long long lda, int ga_off, const float* scale_a, const float* parts, long long ldp,
+                              const float* coef, const int32_t* choice, int n_parts, int n_real, const float* f_dense,
+                              long long ldf, int gf_off, const float* scale_f, const float* norm_w, const float* next_w,
+                              void* h_next, int act_dtype, int T, int D, float eps, int pdl, zl_stream_t stream);
 /* ------------------------------------------------------------------------------------------ *
  * Kodupel: decoder-only model whose layers are listed one by one: the mixer is attention (grouped key/value heads,
  * biased projections, per-head query / key RMS norm, partial rotation in adjacent pairs with YaRN frequencies, value
@@ -743,6 +791,54 @@ int zl_lagelorn_stats(zl_lagelorn_t* m, double* weight_bytes, int* kernels_per_s
 /* Copies one slot's recurrent state of layer `layer` ((heads, dim_k, dim_v) fp32) to the host (tests). */
 int zl_lagelorn_read_state(zl_lagelorn_t* m, int layer, int slot, float* out_host);
 
+/* ------------------------------------------------------------------------------------------ *
+ * Dizizen: decoder-only model of parallel layers on an fp32 residual stream: one RMS norm (weight 1 + w) feeds the
+ * mixer and the feed-forward, each result is scaled per channel (layer scale) and gated by sigmoid(W h + b), and the
+ * sum enters the stream times residual_mult.  The mixer is attention with grouped key/value heads, biased
+ * projections, rotation of queries and keys in halves, values rotated by their own position (cached so) whose summed
+ * output is turned back by the query's position, an ordinary causal softmax, optionally another layer's caches.  The
+ * feed-forward is absent, a dense clamped gated unit with biases, or a mixture of relu^2 experts chosen by softmax
+ * scores plus a correction inside the best groups of router slots, with identity slots that hand the input through
+ * and a shared expert.  Same driver shape as zl_kodupel_*.
+ * ------------------------------------------------------------------------------------------ */
+enum { ZL_FF_NONE = 0, ZL_FF_DENSE = 1, ZL_FF_MOE = 2 };
+typedef struct zl_dizizen zl_dizizen_t;
+typedef struct zl_dizizen_layer {
+    int heads, kv_heads, dim, vdim;
+    int kv_from;           /* -1 own keys and values; j: reads layer j's caches */
+    int rot_dims;          /* rotated dimensions of every query / key head (even, <= dim; 0: none) */
+    float rot_base, scale; /* frequencies base^(-2i/n) for queries / keys (n = rot_dims) and values (n = vdim); score scale */
+    int ff_kind;           /* ZL_FF_* */
+    int ff;                /* inner size of the dense feed-forward or of one expert */
+    float limit;           /* dense: clamp of the gate and up projections */
+    int experts, identity, top, groups, keep; /* router slots = experts + identity, in `groups` groups of which `keep` count */
+    int shared_ff;         /* inner size of the shared expert, 0: none */
+} zl_dizizen_layer_t;
+typedef struct zl_dizizen_config {
+    int num_layers, width, vocab;
+    float eps, embed_scale, residual_mult;
+    int dtype; /* ZL_BF16 or ZL_F32 */
+    int max_batch, max_seq, max_step_tokens;
+    int use_pdl, use_graph;
+} zl_dizizen_config_t;
+int zl_dizizen_create(const zl_dizizen_config_t* cfg, const zl_dizizen_layer_t* layers, zl_dizizen_t** out);
+void zl_dizizen_destroy(zl_dizizen_t* m);
+int zl_dizizen_load_tensor(zl_dizizen_t* m, const char* name, const void* data_host, int rows, int cols, int elem_bytes);
+int zl_dizizen_init_synthetic(zl_dizizen_t* m, uint64_t seed);
+int zl_dizizen_finalize(zl_dizizen_t* m);
+/* Same contract as zl_dekipel_step. */
+int zl_dizizen_step(zl_dizizen_t* m, const int32_t* tokens_host, const int32_t* slots_host, const int32_t* positions_host,
+                    int T, const int32_t* want_rows_host, int n_want, float* logits_host, int32_t* next_host);
+int zl_dizizen_set_state(zl_dizizen_t* m, const int32_t* tokens_host, const int32_t* positions_host, int B);
+int zl_dizizen_step_device(zl_dizizen_t* m, int B);
+int zl_dizizen_sync(zl_dizizen_t* m);
+zl_stream_t zl_dizizen_stream(zl_dizizen_t* m);
+int zl_dizizen_capture_layers(zl_dizizen_t* m, int on);
+int zl_dizizen_read_layers(zl_dizizen_t* m, float* out_host, int T);
+int zl_dizizen_stats(zl_dizizen_t* m, double* weight_bytes, int* kernels_per_step);
+/* Copies rows 0 .. n_rows of one slot's key and value caches of a layer that owns them to the host as fp32:
+ * keys (n_rows, kv_heads * dim), values (n_rows, kv_heads * vdim) (tests). */
+int zl_dizizen_read_cache(zl_dizizen_t* m, int layer, int slot, int n_rows, float* keys_host, float* values_host);
 #ifdef __cplusplus
 }
 #endif

@@ -92,6 +92,8 @@ def parse_header(path=HEADER):
     src = re.sub(r"typedef struct zl_kodupel_config \{.*?\} zl_kodupel_config_t;", " ", src, flags=re.S)
     src = re.sub(r"typedef struct zl_lagelorn_layer \{.*?\} zl_lagelorn_layer_t;", " ", src, flags=re.S)
     src = re.sub(r"typedef struct zl_lagelorn_config \{.*?\} zl_lagelorn_config_t;", " ", src, flags=re.S)
+    src = re.sub(r"typedef struct zl_dizizen_layer \{.*?\} zl_dizizen_layer_t;", " ", src, flags=re.S)
+    src = re.sub(r"typedef struct zl_dizizen_config \{.*?\} zl_dizizen_config_t;", " ", src, flags=re.S)
     src = re.sub(r"enum \{.*?\};", " ", src, flags=re.S)
     protos = {}
     for m in re.finditer(r"([A-Za-z_][\w \*]*?)\b(zl_\w+)\s*\(([^;{}]*?)\)\s*;", src):

@@ -35,6 +35,7 @@ FAMILY_SOURCES = {
     "kodupel": _FP32_RESIDUAL_COMMON + ["mixer_rows", "moe_route", "delta_rule", "sink_attn", "kodupel_runner"],
     "dekipel": _FP32_RESIDUAL_COMMON + ["latent_attn", "dekipel_runner"],
     "lagelorn": _FP32_RESIDUAL_COMMON + ["mixer_rows", "delta_rule", "sink_attn", "lagelorn_runner"],
+    "dizizen": _FP32_RESIDUAL_COMMON + ["mixer_rows", "moe_route", "sink_attn", "dizizen_runner"],
 }
 
 

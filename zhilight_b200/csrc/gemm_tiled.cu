@@ -34,6 +34,7 @@ struct GemmP {
                                       // soft cap: limit * tanh(v / limit)
     int pair_gelu = 0;                // few-rows kernel with a gated unit: gelu_tanh(gate) * up instead of the clamped unit
     int act_gelu_mul = 0;             // few-rows kernel without the gated unit: gelu_tanh of the (biased) sum times gate[m][n]
+    int act_relu2 = 0;                // few-rows kernel without the gated unit: max(sum, 0)^2
 };
 
 __host__ __device__ constexpr bool epi_pairs(int epi) { return epi == ZL_GEMM_EPI_GLU_CLAMP || epi == ZL_GEMM_EPI_GEGLU_TANH; }
@@ -377,6 +378,7 @@ __global__ void __launch_bounds__(256) k_gemm_grouped_small(GemmP p) {
                 } else {
                     if (p.bias) v += p.bias[(size_t)b * p.bb + n];
                     if (p.act_tanh) v = tanhf(v);
+                    if (p.act_relu2) v = fmaxf(v, 0.f), v *= v;
                     if (p.act_gelu_mul && m < mc) v = gelu_f(v) * p.gate[(size_t)(first + m0 + m) * p.ldg + n];
                 }
                 if (lane == m) mine = v;
@@ -570,16 +572,17 @@ static int gemm_dispatch(GemmP p, int batch, int in_dtype, int out_dtype, int ep
         else
             e = launch(k_gemm_f32<ZL_GEMM_EPI_NONE>, grid, block, 0, stream, pdl != 0, p, (int)vx, (int)vw);
     } else if (grouped && M <= grouped_small_max() && vx && vw && K % 8 == 0 && (size_t)8 * K * 2 <= 160 * 1024 &&
-               (epilogue == ZL_GEMM_EPI_NONE || pairs)) {   // a decode step's experts: a handful of rows per group
+               (epilogue == ZL_GEMM_EPI_NONE || epilogue == ZL_GEMM_EPI_RELU2 || pairs)) {   // a decode step's experts: a handful of rows per group
+        p.act_relu2 = epilogue == ZL_GEMM_EPI_RELU2;
         if (in_dtype == ZL_BF16)
             e = out_dtype == ZL_F32 ? launch_grouped_small<__nv_bfloat16, float>(p, batch, pairs, pdl != 0, stream)
                                     : launch_grouped_small<__nv_bfloat16, __nv_bfloat16>(p, batch, pairs, pdl != 0, stream);
         else
             e = out_dtype == ZL_F32 ? launch_grouped_small<__half, float>(p, batch, pairs, pdl != 0, stream)
                                     : launch_grouped_small<__half, __half>(p, batch, pairs, pdl != 0, stream);
-    } else if (!grouped && epilogue == ZL_GEMM_EPI_GEGLU_TANH && batch == 1 && M <= 8 && vx && vw && K % 8 == 0 &&
+    } else if (!grouped && pairs && batch == 1 && M <= 8 && vx && vw && K % 8 == 0 &&
                (size_t)8 * K * 2 <= 160 * 1024) {   // a dense gated feed-forward of a decode step: gate and up rows streamed together
-        p.pair_gelu = 1;
+        p.pair_gelu = epilogue == ZL_GEMM_EPI_GEGLU_TANH;
         if (in_dtype == ZL_BF16)
             e = out_dtype == ZL_F32 ? launch_grouped_small<__nv_bfloat16, float>(p, 1, true, pdl != 0, stream)
                                     : launch_grouped_small<__nv_bfloat16, __nv_bfloat16>(p, 1, true, pdl != 0, stream);
@@ -644,12 +647,23 @@ extern "C" int zl_gemm_nt_bias(const void* x, long long ldx, const void* w, long
     return gemm_dispatch(p, 1, in_dtype, out_dtype, epilogue, pdl, stream);
 }
 
+extern "C" int zl_gemm_nt_glu_clamp(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* y,
+                                    long long ldy, int M, int N, int K, int in_dtype, int out_dtype, float limit, float alpha,
+                                    float beta, int pdl, zl_stream_t stream) {
+    GemmP p{x, w, y, nullptr, ldx, 0, ldw, 0, ldy, 0, 0, 0, M, N, K};
+    p.bias = bias;
+    p.limit = limit;
+    p.alpha = alpha;
+    p.beta = beta;
+    return gemm_dispatch(p, 1, in_dtype, out_dtype, ZL_GEMM_EPI_GLU_CLAMP, pdl, stream);
+}
+
 extern "C" int zl_gemm_nt_grouped(const void* x, long long ldx, const int32_t* x_rows, const void* w, long long ldw,
                                   long long w_group_stride, void* y, long long ldy, const int32_t* y_rows,
                                   const int32_t* group_offsets, int groups, int max_rows, int N, int K, int in_dtype,
                                   int out_dtype, int epilogue, float limit, float alpha, float beta, int pdl,
                                   zl_stream_t stream) {
-    ZL_CHECK_ARG(group_offsets && (epilogue == ZL_GEMM_EPI_NONE || epilogue == ZL_GEMM_EPI_GLU_CLAMP));
+    ZL_CHECK_ARG(group_offsets && (epilogue == ZL_GEMM_EPI_NONE || epilogue == ZL_GEMM_EPI_RELU2 || epilogue == ZL_GEMM_EPI_GLU_CLAMP));
     GemmP p{x, w, y, nullptr, ldx, 0, ldw, w_group_stride, ldy, 0, 0, 0, max_rows, N, K};
     p.grp_off = group_offsets;
     p.x_rows = x_rows;

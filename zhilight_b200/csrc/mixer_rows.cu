@@ -11,7 +11,11 @@
 //     projection kept as the value, and the append to the slot's caches;
 //   * the mixes of a token with its predecessor, x + (x_prev - x) * mu_s for several coefficient vectors mu_s at once (the
 //     predecessor is the previous row of the run or the slot's stored last token);
-//   * norm after the sum: x <- w * rms(alpha x + c_a a + c_b b).
+//   * norm after the sum: x <- w * rms(alpha x + c_a a + c_b b);
+//   * rotations from a per-step (cos, sin) table: queries and keys over their first rot_dims dimensions and values over
+//     all of theirs, pairs in halves or adjacent, no norms, with the append to the slot's caches;
+//   * the residual update of a parallel layer: both sublayers' results times a layer scale and a sigmoid gate per channel,
+//     the second a weighted sum of parts of which some may be the sublayers' input itself, then the next layer's norm.
 #include "common.cuh"
 
 #include <cmath>
@@ -341,9 +345,227 @@ __global__ void __launch_bounds__(256) k_postnorm_combine(float* __restrict__ x,
     }
 }
 
+// table[t][i] = (cos, sin)(pos[t] * inv_freq[i]): the angle and its functions in double (at position 1000 a float angle is
+// already off by 3e-5 rad), once per step for every kernel that turns by these angles
+__global__ void __launch_bounds__(256) k_rope_table(const int32_t* __restrict__ pos, const double* __restrict__ inv_freq,
+                                                    float2* __restrict__ table, int T, int half) {
+    pdl_trigger();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * half) return;
+    const int t = i / half;
+    double sd, cd;
+    sincos((double)pos[t] * inv_freq[i - t * half], &sd, &cd);
+    table[i] = make_float2((float)cd, (float)sd);
+}
+
+struct QkvRopeP {
+    const float* proj;
+    long long ldp;
+    int q_off, k_off, v_off;   // k_off < 0: the layer has no keys / values of its own
+    int H, G, d, vd, rot_dims, layout;
+    const float2* qk_table;    // (T, rot_dims / 2)
+    const float2* v_table;     // (T, vd / 2) or null: values are stored as projected
+    void* q_out;               // (T, H * d)
+    void* const* k_addrs;      // slot -> (max_seq, G, d)
+    void* const* v_addrs;      // slot -> (max_seq, G, vd)
+    const int32_t *slot, *pos;
+};
+
+// one warp per (token, unit); units: H query heads, then G key heads, then G value heads.  grid (ceil(units / 4), T).
+// No norms: the unit's first `rot` channels turn pair by pair by the token's table row, the rest pass.
+template <typename TO>
+__global__ void __launch_bounds__(128) k_qkv_rope_append(QkvRopeP p) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int unit = blockIdx.x * 4 + warp;
+    const int units = p.H + (p.k_off >= 0 ? 2 * p.G : 0);
+    if (unit >= units) return;
+    const float* row = p.proj + (size_t)t * p.ldp;
+    const float* src;
+    const float2* tab;
+    TO* dst;
+    int n, rot;
+    if (unit < p.H) {
+        src = row + p.q_off + (size_t)unit * p.d;
+        n = p.d, rot = p.rot_dims;
+        tab = p.qk_table + (size_t)t * (p.rot_dims >> 1);
+        dst = static_cast<TO*>(p.q_out) + ((size_t)t * p.H + unit) * p.d;
+    } else if (unit < p.H + p.G) {
+        const int g = unit - p.H;
+        src = row + p.k_off + (size_t)g * p.d;
+        n = p.d, rot = p.rot_dims;
+        tab = p.qk_table + (size_t)t * (p.rot_dims >> 1);
+        dst = static_cast<TO*>(p.k_addrs[p.slot[t]]) + ((size_t)p.pos[t] * p.G + g) * p.d;
+    } else {
+        const int g = unit - p.H - p.G;
+        src = row + p.v_off + (size_t)g * p.vd;
+        n = p.vd, rot = p.v_table ? p.vd : 0;
+        tab = p.v_table + (size_t)t * (p.vd >> 1);
+        dst = static_cast<TO*>(p.v_addrs[p.slot[t]]) + ((size_t)p.pos[t] * p.G + g) * p.vd;
+    }
+    const int half = rot >> 1;
+    for (int i = lane; i < half; i += 32) {
+        const int c1 = p.layout == ZL_ROT_ADJACENT ? 2 * i : i, c2 = p.layout == ZL_ROT_ADJACENT ? 2 * i + 1 : i + half;
+        const float u = src[c1], v = src[c2];
+        const float2 cs = tab[i];
+        dst[c1] = from_f32<TO>(u * cs.x - v * cs.y);
+        dst[c2] = from_f32<TO>(v * cs.x + u * cs.y);
+    }
+    for (int c = rot + lane; c < n; c += 32) dst[c] = from_f32<TO>(src[c]);
+}
+
+struct GatedCombineP {
+    float* x;
+    long long ldx;
+    float mult;
+    const float* gates;        // gate logits of both sublayers in one row: [ga_off .. + D), [gf_off .. + D)
+    long long ldg;
+    const float* a;            // first sublayer's result (T, D)
+    long long lda;
+    int ga_off;
+    const float* scale_a;
+    const float* parts;        // second sublayer: n_parts rows per token, or null
+    long long ldp;
+    const float* coef;         // (T, n_parts) or null: ones
+    const int32_t* choice;     // (T, n_parts) or null; entries >= n_real stand for the sublayers' input itself
+    int n_parts, n_real;
+    const float* f_dense;      // one more row per token added to the second sublayer's sum, or null
+    long long ldf;
+    int gf_off;
+    const float* scale_f;
+    const float* norm_w;       // multipliers of the norm the sublayers read (for the handed-through input)
+    const float* next_w;       // multipliers of the next norm, or null
+    void* h_next;
+    int D;
+    float eps;
+};
+
+__device__ __forceinline__ float block_sum_256(float v, float* red) {
+    v = warp_sum(v);
+    __syncthreads();   // red may still be read from an earlier sum
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    return tot;
+}
+
+// x[t] += mult * (scale_a sigmoid(g_a) a[t] + scale_f sigmoid(g_f) f[t]), f[t] = sum_p coef_p * (part_p or the sublayers'
+// input norm_w * rms(x_old)) + f_dense[t], the parts added in the order of p; then the next layer's norm of the new x.
+// One CTA per token; dynamic shared memory D floats (the new x between the two passes).
+template <typename TO>
+__global__ void __launch_bounds__(256) k_gated_parallel_combine(GatedCombineP p) {
+    extern __shared__ float gsx[];
+    __shared__ float red[8];
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, D = p.D;
+    float* xr = p.x + (size_t)t * p.ldx;
+    const float* gr = p.gates + (size_t)t * p.ldg;
+    const bool second = p.parts || p.f_dense;
+    const int32_t* ch = p.choice ? p.choice + (size_t)t * p.n_parts : nullptr;
+    const float* cf = p.coef ? p.coef + (size_t)t * p.n_parts : nullptr;
+    bool through = false;
+    if (p.parts && ch)
+        for (int q = 0; q < p.n_parts; ++q) through |= ch[q] >= p.n_real;
+    float r_old = 0.f;
+    if (through) {   // uniform over the CTA
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < D; c += 256) ss = fmaf(xr[c], xr[c], ss);
+        r_old = 1.0f / sqrtf(block_sum_256(ss, red) / (float)D + p.eps);
+    }
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < D; c += 256) {
+        const float xv = xr[c];
+        float s = p.scale_a[c] * (1.0f / (1.0f + expf(-gr[p.ga_off + c]))) * p.a[(size_t)t * p.lda + c];
+        if (second) {
+            float f = 0.f;
+            if (p.parts)
+                for (int q = 0; q < p.n_parts; ++q) {
+                    const float v = (ch && ch[q] >= p.n_real) ? xv * r_old * p.norm_w[c] : p.parts[((size_t)t * p.n_parts + q) * p.ldp + c];
+                    f = fmaf(cf ? cf[q] : 1.0f, v, f);
+                }
+            if (p.f_dense) f += p.f_dense[(size_t)t * p.ldf + c];
+            s = fmaf(p.scale_f[c] * (1.0f / (1.0f + expf(-gr[p.gf_off + c]))), f, s);
+        }
+        const float nx = fmaf(p.mult, s, xv);
+        xr[c] = nx;
+        gsx[c] = nx;
+        ss = fmaf(nx, nx, ss);
+    }
+    if (!p.next_w) return;
+    const float r = 1.0f / sqrtf(block_sum_256(ss, red) / (float)D + p.eps);
+    TO* h = static_cast<TO*>(p.h_next) + (size_t)t * D;
+    for (int c = threadIdx.x; c < D; c += 256) h[c] = from_f32<TO>(gsx[c] * r * p.next_w[c]);
+}
+
 }  // namespace zl
 
 using namespace zl;
+
+extern "C" int zl_rope_table(const int32_t* pos, int T, const double* inv_freq, int half, float* table, int pdl,
+                             zl_stream_t stream) {
+    ZL_CHECK_ARG(pos && inv_freq && table && T > 0 && half > 0 && (reinterpret_cast<uintptr_t>(table) & 7) == 0);
+    ZL_CHECK_CUDA(launch(k_rope_table, dim3(cdiv(T * half, 256)), dim3(256), 0, stream, pdl != 0, pos, inv_freq,
+                         reinterpret_cast<float2*>(table), T, half));
+    return ZL_OK;
+}
+
+extern "C" int zl_qkv_table_rope_append(const float* proj, long long ldp, int q_off, int k_off, int v_off, int heads, int kv_heads,
+                                  int dim, int vdim, const float* qk_table, int rot_dims, const float* v_table, int layout,
+                                  void* q_out, void* const* k_addrs, void* const* v_addrs, const int32_t* slot,
+                                  const int32_t* pos, int T, int dtype, int pdl, zl_stream_t stream) {
+    ZL_CHECK_ARG(proj && q_out && slot && pos && T > 0 && T <= 65535 && heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0);
+    ZL_CHECK_ARG(rot_dims >= 0 && rot_dims <= dim && rot_dims % 2 == 0 && (rot_dims == 0 || qk_table));
+    ZL_CHECK_ARG(k_off < 0 || (k_addrs && v_addrs && (!v_table || vdim % 2 == 0)));
+    ZL_CHECK_ARG(layout == ZL_ROT_HALVES || layout == ZL_ROT_ADJACENT);
+    ZL_CHECK_ARG(dtype == ZL_F16 || dtype == ZL_BF16 || dtype == ZL_F32);
+    QkvRopeP p{proj, ldp, q_off, k_off, v_off, heads, kv_heads, dim, vdim, rot_dims, layout,
+               reinterpret_cast<const float2*>(qk_table), reinterpret_cast<const float2*>(v_table), q_out, k_addrs, v_addrs, slot, pos};
+    const int units = heads + (k_off >= 0 ? 2 * kv_heads : 0);
+    const dim3 grid(cdiv(units, 4), T), block(128);
+    cudaError_t e;
+    if (dtype == ZL_F32) e = launch(k_qkv_rope_append<float>, grid, block, 0, stream, pdl != 0, p);
+    else if (dtype == ZL_BF16) e = launch(k_qkv_rope_append<__nv_bfloat16>, grid, block, 0, stream, pdl != 0, p);
+    else e = launch(k_qkv_rope_append<__half>, grid, block, 0, stream, pdl != 0, p);
+    ZL_CHECK_CUDA(e);
+    return ZL_OK;
+}
+
+extern "C" int zl_gated_parallel_combine(float* x, long long ldx, float mult, const float* gates, long long ldg, const float* a,
+                                         long long lda, int ga_off, const float* scale_a, const float* parts, long long ldp,
+                                         const float* coef, const int32_t* choice, int n_parts, int n_real, const float* f_dense,
+                                         long long ldf, int gf_off, const float* scale_f, const float* norm_w,
+                                         const float* next_w, void* h_next, int act_dtype, int T, int D, float eps, int pdl,
+                                         zl_stream_t stream) {
+    ZL_CHECK_ARG(x && gates && a && scale_a && T > 0 && D > 0 && ldx >= D && lda >= D && ga_off >= 0);
+    ZL_CHECK_ARG(!parts || (n_parts > 0 && ldp >= D && (!choice || norm_w)));
+    ZL_CHECK_ARG(!(parts || f_dense) || (scale_f && gf_off >= 0));
+    ZL_CHECK_ARG(!f_dense || ldf >= D);
+    ZL_CHECK_ARG(!next_w || (h_next && (act_dtype == ZL_F16 || act_dtype == ZL_BF16 || act_dtype == ZL_F32)));
+    GatedCombineP p{x, ldx, mult, gates, ldg, a, lda, ga_off, scale_a, parts, ldp, coef, choice, n_parts, n_real, f_dense, ldf,
+                    gf_off, scale_f, norm_w, next_w, h_next, D, eps};
+    const size_t smem = (size_t)D * sizeof(float);
+    ZL_CHECK_SUPPORTED(smem <= 200 * 1024);
+    cudaError_t e = cudaSuccess;
+    static size_t set_for[3] = {0, 0, 0};
+    const int ti = act_dtype == ZL_F32 ? 0 : (act_dtype == ZL_BF16 ? 1 : 2);
+    if (smem > 48 * 1024 && smem > set_for[ti]) {
+        if (ti == 0) e = cudaFuncSetAttribute(k_gated_parallel_combine<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        else if (ti == 1) e = cudaFuncSetAttribute(k_gated_parallel_combine<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        else e = cudaFuncSetAttribute(k_gated_parallel_combine<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        ZL_CHECK_CUDA(e);
+        set_for[ti] = smem;
+    }
+    if (ti == 0) e = launch(k_gated_parallel_combine<float>, dim3(T), dim3(256), smem, stream, pdl != 0, p);
+    else if (ti == 1) e = launch(k_gated_parallel_combine<__nv_bfloat16>, dim3(T), dim3(256), smem, stream, pdl != 0, p);
+    else e = launch(k_gated_parallel_combine<__half>, dim3(T), dim3(256), smem, stream, pdl != 0, p);
+    ZL_CHECK_CUDA(e);
+    return ZL_OK;
+}
 
 extern "C" int zl_qk_fullnorm_append(const float* proj, long long ldp, int q_off, int k_off, int heads, int kv_heads, int dim,
                                      const float* q_weight, const float* k_weight, float eps, void* q_out, void* const* k_addrs,

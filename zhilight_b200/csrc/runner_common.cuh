@@ -1,4 +1,4 @@
-// Host-side pieces shared by the model drivers (llama_runner.cu, dekipel_runner.cu, kodupel_runner.cu): staged checkpoint tensors,
+// Host-side pieces shared by the model drivers (llama_runner.cu, dekipel_runner.cu, kodupel_runner.cu, ...): staged checkpoint tensors,
 // device allocation helpers, and the slot cache -- the per-task, per-layer row buffers every driver appends to and
 // its kernels reach through a device table of slot base pointers (the reference's per-task buffer tables,
 // src/model/rag_buffer_context.h:141-181).
@@ -213,5 +213,88 @@ int stage_random(M* m, const std::string& name, int rows, int cols, float lo, fl
     return ZL_OK;
 }
 
+
+// ---- load helpers of drivers whose checkpoints keep norm weights around zero, biases per projection and gate / up pairs ---
+static __global__ void k_add_const(float* w, int n, float v) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) w[i] += v;
+}
+// dst rows 2j / 2j+1 <- a row j / b row j; a, b are (rows, cols) each
+template <typename TS, typename TD>
+__global__ void k_interleave_pair_rows(const TS* __restrict__ a, const TS* __restrict__ b, TD* __restrict__ dst, int rows, int cols) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)rows * cols) return;
+    const size_t j = i / cols, c = i % cols;
+    dst[(2 * j) * cols + c] = from_f32<TD>(to_f32<TS>(a[i]));
+    dst[(2 * j + 1) * cols + c] = from_f32<TD>(to_f32<TS>(b[i]));
+}
+
+// checkpoint norm tensor w -> fp32 array of the multipliers 1 + w
+template <typename M>
+int take_norm_plus_one(M* m, const std::string& name, int n, float** out) {
+    RCHECK(take_f32(m, name, 1, n, out));
+    k_add_const<<<cdiv(n, 256), 256, 0, m->stream>>>(*out, n, 1.0f);
+    ZL_CHECK_LAUNCH();
+    ZL_CHECK_CUDA(cudaStreamSynchronize(m->stream));
+    return ZL_OK;
+}
+
+// bias segment `name` (n) -> fp32 bias array at offset off
+template <typename M>
+int put_bias_f32(M* m, const std::string& name, int n, float* dst, int off) {
+    const Staged* s = need(m, name, 1, n);
+    if (!s) return ZL_ERR_STATE;
+    RCHECK(convert_to<float>(m, s, dst + off, (size_t)n));
+    ZL_CHECK_CUDA(cudaStreamSynchronize(m->stream));
+    staged_drop(m->staged, name);
+    return ZL_OK;
+}
+
+// fp32 bias -> a copy in the activation dtype (16-bit modes; checkpoint biases are 16-bit, so nothing is lost)
+template <typename M>
+int bias_copy_act(M* m, const float* src, int n, void** out) {
+    if (m->cfg.dtype == ZL_F32) return ZL_OK;
+    RCHECK(dmalloc(out, (size_t)n * 2));
+    k_convert<float, __nv_bfloat16><<<cdiv(n, 256), 256, 0, m->stream>>>(src, static_cast<__nv_bfloat16*>(*out), (size_t)n);
+    ZL_CHECK_LAUNCH();
+    ZL_CHECK_CUDA(cudaStreamSynchronize(m->stream));
+    return ZL_OK;
+}
+
+// tensors `a` and `b` (rows, cols) -> dst (2 * rows, cols) at element offset off with their rows interleaved (a gated unit's
+// gate / up pairs as the GEMM epilogues want them); dst_f32: dst is fp32 whatever the activation dtype (biases)
+template <typename M>
+int put_interleaved(M* m, const std::string& a, const std::string& b, int rows, int cols, void* dst, size_t off, bool dst_f32) {
+    const Staged* sa = need(m, a, rows, cols);
+    const Staged* sb = need(m, b, rows, cols);
+    if (!sa || !sb) return ZL_ERR_STATE;
+    if (sa->elem != sb->elem) {
+        zl_set_last_error(__FILE__, __LINE__, ("tensors of a pair differ in dtype: " + a).c_str());
+        return ZL_ERR_STATE;
+    }
+    const size_t n = (size_t)rows * cols;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    const bool f32 = dst_f32 || m->cfg.dtype == ZL_F32;
+    if (f32) {
+        if (sa->elem == 2)
+            k_interleave_pair_rows<<<blocks, 256, 0, m->stream>>>((const __nv_bfloat16*)sa->ptr, (const __nv_bfloat16*)sb->ptr,
+                                                                  (float*)dst + off, rows, cols);
+        else
+            k_interleave_pair_rows<<<blocks, 256, 0, m->stream>>>((const float*)sa->ptr, (const float*)sb->ptr, (float*)dst + off, rows, cols);
+    } else {
+        if (sa->elem == 2)
+            k_interleave_pair_rows<<<blocks, 256, 0, m->stream>>>((const __nv_bfloat16*)sa->ptr, (const __nv_bfloat16*)sb->ptr,
+                                                                  (__nv_bfloat16*)dst + off, rows, cols);
+        else
+            k_interleave_pair_rows<<<blocks, 256, 0, m->stream>>>((const float*)sa->ptr, (const float*)sb->ptr,
+                                                                  (__nv_bfloat16*)dst + off, rows, cols);
+    }
+    ZL_CHECK_LAUNCH();
+    ZL_CHECK_CUDA(cudaStreamSynchronize(m->stream));
+    staged_drop(m->staged, a);
+    staged_drop(m->staged, b);
+    if (!dst_f32) m->weight_bytes += 2.0 * n * m->esz;
+    return ZL_OK;
+}
 
 }  // namespace zl

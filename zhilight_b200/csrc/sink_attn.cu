@@ -4,7 +4,9 @@
 // appended before this runs, so prompts, portions of prompts and single decode tokens are the same case.
 // Two optional restrictions of the general form: with chunk > 0 a token sees only the keys of its own block of `chunk`
 // positions (blocks counted from position 0 of the sequence), and with a distance table the score of (token, key)
-// gets dist_bias[h][min(pos - key, n_dist - 1)] added after the scale.
+// gets dist_bias[h][min(pos - key, n_dist - 1)] added after the scale.  Two more options: no sink at all (an ordinary
+// softmax), and an output rotation: values that were cached turned by their own position give a sum that is turned back
+// by the query's position, pair by pair from a (cos, sin) table, in fp32 before the store.
 //
 // k_sink_attn_mma (16-bit caches, head sizes that are multiples of 16, values up to 128 wide, at most 16 query heads per
 // key/value head): a CTA owns up to 64 rows = (consecutive tokens of one run) x (the query heads of one key/value
@@ -42,7 +44,22 @@ struct SinkAttnP {
     int chunk = 0;             // > 0: keys below (pos / chunk) * chunk are not seen
     const float* dist_bias = nullptr;   // (H, n_dist) added to the scaled score by distance, or null
     int n_dist = 0;
+    int no_sink = 0;           // the denominator holds the keys only
+    const float* out_table = nullptr;   // (T, vd / 2) pairs (cos, sin): the output of token t is turned back by these angles
+    int out_layout = 0;        // ZL_ROT_HALVES: pair (m, m + vd / 2); ZL_ROT_ADJACENT: pair (2m, 2m + 1)
 };
+
+// the two channels of pair m
+__device__ __forceinline__ void sa_pair(const SinkAttnP& p, int m, int& c1, int& c2) {
+    if (p.out_layout == ZL_ROT_ADJACENT) c1 = 2 * m, c2 = 2 * m + 1;
+    else c1 = m, c2 = m + (p.vd >> 1);
+}
+// (u, v) turned by minus the angle of (cos, sin) = cs, times `mul`, stored
+template <typename T>
+__device__ __forceinline__ void sa_store_unrotated(T* out, int c1, int c2, float u, float v, float2 cs, float mul) {
+    out[c1] = from_f32<T>((u * cs.x + v * cs.y) * mul);
+    out[c2] = from_f32<T>((v * cs.x - u * cs.y) * mul);
+}
 
 // first key a token at `pos` sees
 __device__ __forceinline__ int sa_first_key(const SinkAttnP& p, int pos) { return p.chunk > 0 ? (pos / p.chunk) * p.chunk : 0; }
@@ -113,14 +130,29 @@ __global__ void __launch_bounds__(kSaWarps * 32) k_sink_attn(SinkAttnP p) {
         }
         return;
     }
-    const float sink = p.sink ? p.sink[h] : 0.f;
+    const float sink = p.no_sink ? -INFINITY : (p.sink ? p.sink[h] : 0.f);
     float M = sink;
     for (int w = 0; w < kSaWarps; ++w) M = fmaxf(M, sm_m[w]);
-    float L = expf(sink - M);
+    float L = expf(sink - M);   // 0 without a sink: the token's own key keeps M finite
     for (int w = 0; w < kSaWarps; ++w) L = fmaf(sm_l[w], expf(sm_m[w] - M), L);
     float gate = 1.0f;
     if (p.gate) gate = 1.0f / (1.0f + expf(-p.gate[(size_t)t * p.ldg + h]));
     T* out = static_cast<T*>(p.out) + ((size_t)t * p.H + h) * p.vd;
+    if (p.out_table) {
+        const float2* tab = reinterpret_cast<const float2*>(p.out_table) + (size_t)t * (p.vd >> 1);
+        for (int mi = threadIdx.x; mi < (p.vd >> 1); mi += blockDim.x) {
+            int c1, c2;
+            sa_pair(p, mi, c1, c2);
+            float o1 = 0.f, o2 = 0.f;
+            for (int w = 0; w < kSaWarps; ++w) {
+                const float e = expf(sm_m[w] - M);
+                o1 = fmaf(sm_acc[(size_t)w * p.vd + c1], e, o1);
+                o2 = fmaf(sm_acc[(size_t)w * p.vd + c2], e, o2);
+            }
+            sa_store_unrotated<T>(out, c1, c2, o1, o2, tab[mi], gate / L);
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < p.vd; c += blockDim.x) {
         float o = 0.f;
         for (int w = 0; w < kSaWarps; ++w) o = fmaf(sm_acc[(size_t)w * p.vd + c], expf(sm_m[w] - M), o);
@@ -237,8 +269,8 @@ __global__ void __launch_bounds__(128) k_sink_attn_mma(SinkAttnMmaP pp) {
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
         const float sink = p.sink ? p.sink[head_of[hh] < p.H ? head_of[hh] : 0] : 0.f;
-        m_run[hh] = (DEC || p.splits > 1) ? -1e30f : sink;
-        l_run[hh] = (DEC || p.splits > 1 || tq != 0) ? 0.f : 1.f;   // the sink's exp(sink - m) = 1, held by one thread of the quad
+        m_run[hh] = (DEC || p.splits > 1 || p.no_sink) ? -1e30f : sink;
+        l_run[hh] = (DEC || p.splits > 1 || p.no_sink || tq != 0) ? 0.f : 1.f;   // the sink's exp(sink - m) = 1, held by one thread of the quad
     }
 #pragma unroll
     for (int j = 0; j < NV; ++j)
@@ -370,9 +402,10 @@ __global__ void __launch_bounds__(128) k_sink_attn_mma(SinkAttnMmaP pp) {
         if (tk >= ntok) return;
         const int t = row0 + tk, h = g * R + (r - tk * R);
         const float sink = p.sink ? p.sink[h] : 0.f;
-        float M = p.splits > 1 ? -1e30f : sink;
+        const bool with_sink = p.splits == 1 && !p.no_sink;
+        float M = with_sink ? sink : -1e30f;
         for (int w = 0; w < 4; ++w) M = fmaxf(M, mm[w * 16 + r]);
-        float L = p.splits > 1 ? 0.f : expf(sink - M), wgt[4];
+        float L = with_sink ? expf(sink - M) : 0.f, wgt[4];
         for (int w = 0; w < 4; ++w) {
             wgt[w] = ml[w * 16 + r] > 0.f ? expf(mm[w * 16 + r] - M) : 0.f;
             L = fmaf(ml[w * 16 + r], wgt[w], L);
@@ -390,6 +423,19 @@ __global__ void __launch_bounds__(128) k_sink_attn_mma(SinkAttnMmaP pp) {
             if (p.gate) gate = 1.0f / (1.0f + expf(-p.gate[(size_t)t * p.ldg + h]));
             const float inv = gate / L;
             T* out = static_cast<T*>(p.out) + ((size_t)t * p.H + h) * p.vd;
+            if (p.out_table) {
+                const float2* tab = reinterpret_cast<const float2*>(p.out_table) + (size_t)t * (p.vd >> 1);
+                for (int mi = tid & 7; mi < (p.vd >> 1); mi += 8) {
+                    int c1, c2;
+                    sa_pair(p, mi, c1, c2);
+                    float o1 = 0.f, o2 = 0.f;
+                    for (int w = 0; w < 4; ++w) {
+                        o1 = fmaf(mo[((size_t)w * 16 + r) * (NV * 8) + c1], wgt[w], o1);
+                        o2 = fmaf(mo[((size_t)w * 16 + r) * (NV * 8) + c2], wgt[w], o2);
+                    }
+                    sa_store_unrotated<T>(out, c1, c2, o1, o2, tab[mi], inv);
+                }
+            } else
             for (int c = tid & 7; c < p.vd; c += 8) {
                 float o = 0.f;
                 for (int w = 0; w < 4; ++w) o = fmaf(mo[((size_t)w * 16 + r) * (NV * 8) + c], wgt[w], o);
@@ -397,6 +443,38 @@ __global__ void __launch_bounds__(128) k_sink_attn_mma(SinkAttnMmaP pp) {
             }
         }
     } else {
+    if (p.out_table && p.splits == 1) {
+        // the tile's normalised rows go through shared memory (the key tiles are no longer needed): the two channels of a
+        // pair sit in different threads
+        __syncthreads();
+        float* so = reinterpret_cast<float*>(sa_raw);   // [kTq][vd + 1]
+        const int SP = p.vd + 1, half = p.vd >> 1;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            if (!row_ok[hh]) continue;
+            float gate = 1.0f;
+            if (p.gate) gate = 1.0f / (1.0f + expf(-p.gate[(size_t)(row0 + tok_of[hh]) * p.ldg + head_of[hh]]));
+            const float inv = gate / l_run[hh];
+            float* sr = so + (size_t)(wrow + gq + hh * 8) * SP;
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const int c = 8 * j + 2 * tq;
+                if (c < p.vd) sr[c] = O[j][hh * 2] * inv, sr[c + 1] = O[j][hh * 2 + 1] * inv;
+            }
+        }
+        __syncthreads();
+        for (int i = tid; i < kTq * half; i += 128) {
+            const int r = i / half, mi = i - r * half, tk = r / R;
+            if (tk >= ntok) continue;
+            const int t = row0 + tk, h = g * R + (r - tk * R);
+            int c1, c2;
+            sa_pair(p, mi, c1, c2);
+            const float2 cs = reinterpret_cast<const float2*>(p.out_table)[(size_t)t * half + mi];
+            sa_store_unrotated<T>(static_cast<T*>(p.out) + ((size_t)t * p.H + h) * p.vd, c1, c2, so[(size_t)r * SP + c1],
+                                  so[(size_t)r * SP + c2], cs, 1.0f);
+        }
+        return;
+    }
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
         if (!row_ok[hh]) continue;
@@ -434,6 +512,7 @@ static cudaError_t launch_sink_mma(const SinkAttnMmaP& pp, int runs, int max_run
     const int qr = DEC ? 16 : kTq, nq = qr / (p.H / p.G);
     size_t smem = ((size_t)qr * (p.d + 8) + 2 * (size_t)kTk * (p.d + 8) + 2 * (size_t)kTk * (NV * 8 + 8)) * sizeof(T);
     if (DEC && smem < (size_t)(128 + 64 * NV * 8) * sizeof(float)) smem = (size_t)(128 + 64 * NV * 8) * sizeof(float);
+    if (!DEC && p.out_table && smem < (size_t)kTq * (p.vd + 1) * sizeof(float)) smem = (size_t)kTq * (p.vd + 1) * sizeof(float);
     static size_t set_for = 0;
     if (smem > 48 * 1024 && smem > set_for) {
         const cudaError_t e = cudaFuncSetAttribute(k_sink_attn_mma<T, NV, DEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -465,7 +544,7 @@ __global__ void __launch_bounds__(128) k_sink_attn_merge(SinkAttnP p) {
     if (h >= p.H) return;
     const int stride = 2 + p.vd;
     const float* part = p.ws + ((size_t)t * p.H + h) * p.splits * stride;
-    const float sink = p.sink ? p.sink[h] : 0.f;
+    const float sink = p.no_sink ? -INFINITY : (p.sink ? p.sink[h] : 0.f);
     const float ms = lane < p.splits ? part[(size_t)lane * stride] : -INFINITY;
     const float ls = lane < p.splits ? part[(size_t)lane * stride + 1] : 0.f;
     const float M = fmaxf(sink, warp_max(ms));
@@ -479,6 +558,24 @@ __global__ void __launch_bounds__(128) k_sink_attn_merge(SinkAttnP p) {
     float wv[32];   // every split's weight in every lane: the loads below do not wait for shuffles
 #pragma unroll
     for (int s = 0; s < 32; ++s) wv[s] = __shfl_sync(0xffffffffu, wgt, s);
+    if (p.out_table) {
+        const float2* tab = reinterpret_cast<const float2*>(p.out_table) + (size_t)t * (p.vd >> 1);
+        for (int mi = lane; mi < (p.vd >> 1); mi += 32) {
+            int c1, c2;
+            sa_pair(p, mi, c1, c2);
+            float v1[32], v2[32];
+#pragma unroll
+            for (int s = 0; s < 32; ++s) {
+                v1[s] = s < p.splits ? part[(size_t)s * stride + 2 + c1] : 0.f;
+                v2[s] = s < p.splits ? part[(size_t)s * stride + 2 + c2] : 0.f;
+            }
+            float o1 = 0.f, o2 = 0.f;
+#pragma unroll
+            for (int s = 0; s < 32; ++s) o1 = fmaf(v1[s], wv[s], o1), o2 = fmaf(v2[s], wv[s], o2);
+            sa_store_unrotated<T>(out, c1, c2, o1, o2, tab[mi], gate / L);
+        }
+        return;
+    }
     for (int c = lane; c < p.vd; c += 32) {
         float v[32];
 #pragma unroll
@@ -515,9 +612,9 @@ extern "C" int zl_sink_attention(const void* q, void* const* k_addrs, void* cons
                                  int T, int heads, int kv_heads, int dim, int vdim, int splits, void* workspace,
                                  size_t workspace_bytes, const int32_t* run_row0, const int32_t* run_len, int runs,
                                  int max_run_len, int dtype, int pdl, zl_stream_t stream) {
-    return zl_sink_attention_local(q, k_addrs, v_addrs, slot, pos, sink, gate, ldg, scale, 0, nullptr, 0, out, T, heads, kv_heads,
-                                   dim, vdim, splits, workspace, workspace_bytes, run_row0, run_len, runs, max_run_len, dtype,
-                                   pdl, stream);
+    return zl_sink_attention_ex(q, k_addrs, v_addrs, slot, pos, sink, 0, gate, ldg, scale, 0, nullptr, 0, nullptr, 0, out, T, heads,
+                                kv_heads, dim, vdim, splits, workspace, workspace_bytes, run_row0, run_len, runs, max_run_len,
+                                dtype, pdl, stream);
 }
 
 extern "C" int zl_distance_bias_table(const float* table_host, int rows, int heads, double far, int n_dist, float* out_host) {
@@ -541,7 +638,20 @@ extern "C" int zl_sink_attention_local(const void* q, void* const* k_addrs, void
                                        int dim, int vdim, int splits, void* workspace, size_t workspace_bytes,
                                        const int32_t* run_row0, const int32_t* run_len, int runs, int max_run_len, int dtype,
                                        int pdl, zl_stream_t stream) {
+    return zl_sink_attention_ex(q, k_addrs, v_addrs, slot, pos, sink, 0, gate, ldg, scale, chunk, dist_bias, n_dist, nullptr, 0, out,
+                                T, heads, kv_heads, dim, vdim, splits, workspace, workspace_bytes, run_row0, run_len, runs,
+                                max_run_len, dtype, pdl, stream);
+}
+
+extern "C" int zl_sink_attention_ex(const void* q, void* const* k_addrs, void* const* v_addrs, const int32_t* slot,
+                                    const int32_t* pos, const float* sink, int no_sink, const float* gate, long long ldg,
+                                    float scale, int chunk, const float* dist_bias, int n_dist, const float* out_table,
+                                    int out_layout, void* out, int T, int heads, int kv_heads, int dim, int vdim, int splits,
+                                    void* workspace, size_t workspace_bytes, const int32_t* run_row0, const int32_t* run_len,
+                                    int runs, int max_run_len, int dtype, int pdl, zl_stream_t stream) {
     ZL_CHECK_ARG(chunk >= 0 && (!dist_bias || n_dist > 0));
+    ZL_CHECK_ARG(!out_table || (vdim % 2 == 0 && (out_layout == ZL_ROT_HALVES || out_layout == ZL_ROT_ADJACENT) &&
+                                (reinterpret_cast<uintptr_t>(out_table) & 7) == 0));
     ZL_CHECK_ARG(q && k_addrs && v_addrs && slot && pos && out && T > 0 && T <= 65535 && heads > 0 && kv_heads > 0);
     ZL_CHECK_ARG(heads % kv_heads == 0 && dim > 0 && vdim > 0);
     ZL_CHECK_SUPPORTED(vdim <= 32 * kSaMaxPerLane);
@@ -553,6 +663,9 @@ extern "C" int zl_sink_attention_local(const void* q, void* const* k_addrs, void
     p.chunk = chunk;
     p.dist_bias = dist_bias;
     p.n_dist = n_dist;
+    p.no_sink = no_sink != 0;
+    p.out_table = out_table;
+    p.out_layout = out_layout;
     const dim3 grid(heads, T, splits), block(kSaWarps * 32);
     const size_t smem = ((size_t)dim + 2 * kSaWarps + (size_t)kSaWarps * vdim) * sizeof(float);
     cudaError_t e;

@@ -94,6 +94,16 @@ def _build_lagelorn(config, dtype, max_batch, max_seq, max_step_tokens, **kw):
 register("Lagelorn", _build_lagelorn, ("bfloat16", "float32"))
 
 
+# ---- Dizizen ---------------------------------------------------------------------------------------------------------
+def _build_dizizen(config, dtype, max_batch, max_seq, max_step_tokens, **kw):
+    from .dizizen import DizizenDecoder
+    return DizizenDecoder.from_config_dict(config, dtype=dtype, max_batch=max_batch, max_seq=max_seq,
+                                           max_step_tokens=max_step_tokens, **kw)
+
+
+register("Dizizen", _build_dizizen, ("bfloat16", "float32"))
+
+
 # ---- Llama (HF folder) -----------------------------------------------------------------------------------------------
 _HF_LLAMA_NAMES = [
     (r"^model\.embed_tokens\.weight$", "token_embedding.weight"),
