@@ -710,3 +710,86 @@ def bonus_decay_scan(r, k, v, decay_logit, bonus, run_row0, run_len, slot, pos, 
               heads * dim_k, _p(bonus), _p(run_row0), _p(run_len), run_row0.numel(), _p(slot), _p(pos), _p(state_table), _p(o),
               heads * dim_v, heads, dim_k, dim_v, t, _p(ws), nbytes, 0, _stream())
     return o
+
+
+# ------------------------------------------------------------------ parallel gated layers, rotated values, grouped routing
+ROT_HALVES, ROT_ADJACENT = 0, 1
+
+
+def gemm_nt_glu_clamp(x, w, bias=None, out_dtype=None, limit=1.0, alpha=1.0, beta=0.0):
+    """y (M, N / 2) = g sigmoid(alpha g) (u + beta) over the column pairs (gate, up) of x @ w^T + bias, g = min(gate, limit),
+    u = clamp(up, +-limit); w (N, K) with gate / up rows interleaved, bias (N) fp32 or None."""
+    m, k = x.shape
+    n = w.shape[0]
+    y = torch.empty((m, n // 2), dtype=out_dtype or x.dtype, device=x.device)
+    _lib.call("zl_gemm_nt_glu_clamp", _p(x), k, _p(w), k, _p(bias), _p(y), n // 2, m, n, k, _dt(x), _dt(y), limit, alpha, beta, 0,
+              _stream())
+    return y
+
+
+def moe_route_grouped(x, w_router, correction, top, groups=1, keep=1, score_fn=MOE_SCORE_SOFTMAX, renormalize=True,
+                      renorm_eps=0.0):
+    """moe_route with the choice restricted to the `keep` best of `groups` groups of neighbouring slots.  w_router None:
+    x (T, slots) already holds the logits."""
+    t, d = x.shape
+    e = w_router.shape[0] if w_router is not None else d
+    dev = x.device
+    te = torch.empty((t, top), dtype=torch.int32, device=dev)
+    tw = torch.empty((t, top), dtype=torch.float32, device=dev)
+    off = torch.empty(e + 1, dtype=torch.int32, device=dev)
+    lt = torch.empty(t * top, dtype=torch.int32, device=dev)
+    lp = torch.empty(t * top, dtype=torch.int32, device=dev)
+    _lib.call("zl_moe_route_grouped", _p(x), d, _p(w_router), _p(correction), _p(te), _p(tw), _p(off), _p(lt), _p(lp), t, d, e,
+              top, groups, keep, score_fn, int(renormalize), renorm_eps, 0, _stream())
+    return te, tw, off, lt, lp
+
+
+def rope_table(pos, inv_freq):
+    """pos (T) int32, inv_freq (half) float64 device tensors -> (T, half, 2) fp32 (cos, sin) of pos * inv_freq."""
+    t, half = pos.numel(), inv_freq.numel()
+    out = torch.empty((t, half, 2), dtype=torch.float32, device=pos.device)
+    _lib.call("zl_rope_table", _p(pos), t, ctypes.cast(_p(inv_freq), ctypes.POINTER(ctypes.c_double)), half, _p(out), 0, _stream())
+    return out
+
+
+def qkv_table_rope_append(proj, q_off, k_off, v_off, heads, kv_heads, dim, vdim, qk_table, rot_dims, v_table, layout, k_slots,
+                          v_slots, slot, pos, dtype):
+    """proj (T, ld) fp32 -> q (T, heads * dim) of `dtype` turned by qk_table; keys (turned alike) and values (turned over vdim
+    by v_table, None: as projected) go to rows (slot, pos) of the caches behind the slot tables unless k_off < 0."""
+    t, ldp = proj.shape
+    q = torch.empty((t, heads * dim), dtype=dtype, device=proj.device)
+    _lib.call("zl_qkv_table_rope_append", _p(proj), ldp, q_off, k_off, v_off, heads, kv_heads, dim, vdim, _p(qk_table), rot_dims,
+              _p(v_table), layout, _p(q), _p(k_slots), _p(v_slots), _p(slot), _p(pos), t, _dt(q), 0, _stream())
+    return q
+
+
+def sink_attention_ex(q, k_table, v_table, slot, pos, scale, heads, kv_heads, dim, vdim, sink=None, no_sink=False, gate=None,
+                      chunk=0, dist_bias=None, out_table=None, out_layout=ROT_HALVES, splits=1, run_row0=None, run_len=None,
+                      max_run_len=0):
+    """sink_attention_local with an ordinary softmax (no_sink) and / or every head's output turned back by out_table
+    ((T, vdim / 2, 2) fp32 from rope_table)."""
+    t = q.shape[0]
+    lib = _lib.load()
+    nbytes = lib.zl_sink_attention_workspace_bytes(t, heads, vdim, splits)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
+    out = torch.empty((t, heads * vdim), dtype=q.dtype, device=q.device)
+    _lib.call("zl_sink_attention_ex", _p(q), _p(k_table), _p(v_table), _p(slot), _p(pos), _p(sink), int(no_sink), _p(gate),
+              gate.shape[1] if gate is not None else 0, scale, chunk, _p(dist_bias),
+              dist_bias.shape[1] if dist_bias is not None else 0, _p(out_table), out_layout, _p(out), t, heads, kv_heads, dim, vdim,
+              splits, _p(ws), nbytes, _p(run_row0), _p(run_len), run_row0.numel() if run_row0 is not None else 0, max_run_len,
+              _dt(q), 0, _stream())
+    return out
+
+
+def gated_parallel_combine(x, mult, gates, ga_off, a, scale_a, eps, parts=None, coef=None, choice=None, n_real=0, f_dense=None,
+                           gf_off=0, scale_f=None, norm_w=None, next_w=None, act_dtype=torch.float32):
+    """x (T, D) fp32 += mult * (scale_a sigmoid(gates[:, ga_off:ga_off + D]) a + scale_f sigmoid(gates[:, gf_off:gf_off + D]) f),
+    f = sum_p coef[:, p] * (parts[:, p], or norm_w * rms(x) where choice[:, p] >= n_real) + f_dense; parts (T, P, D) fp32.
+    Returns next_w * rms(new x) in act_dtype when next_w is given."""
+    t, d = x.shape
+    n_parts = parts.shape[1] if parts is not None else 0
+    h = torch.empty((t, d), dtype=act_dtype, device=x.device) if next_w is not None else None
+    _lib.call("zl_gated_parallel_combine", _p(x), d, mult, _p(gates), gates.shape[1], _p(a), d, ga_off, _p(scale_a), _p(parts), d,
+              _p(coef), _p(choice), n_parts, n_real, _p(f_dense), d, gf_off, _p(scale_f), _p(norm_w), _p(next_w), _p(h),
+              _dt(h) if h is not None else F32, t, d, eps, 0, _stream())
+    return h
