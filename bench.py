@@ -687,6 +687,128 @@ def run_compare_lagelorn(args):
                       "timing": "CUDA events on the model's stream; weights per pass larger than L2"}))
 
 
+# ----------------------------------------------------------------------------------------------------------------------
+# --compare-dizizen: prefill and decode throughput of the Dizizen family beside Kodupel (the closest existing model:
+# attention over slot caches with shared caches, routed experts, an fp32 residual stream, the same GEMM / attention /
+# routing kernels) at equal width, depth, heads and equal feed-forward parameters per token, random weights.  Does not
+# touch the default workload.
+# ----------------------------------------------------------------------------------------------------------------------
+def _dizizen_config(sz):
+    """Layers: dense / experts on the first layer's cache / dense / experts on the third's.  An expert has two matrices
+    where Kodupel's has three: `top` experts of ff_e plus a shared one of 2 * ff_e use what Kodupel's `top` experts use."""
+    att = dict(heads=sz["heads"], kv_heads=8, dim=sz["dim"], vdim=sz["dim"], scale=sz["dim"] ** -0.5,
+               rot={"base": 5e5, "dims": sz["dim"] // 2})
+    moe = {"kind": "moe", "expert": {"ff": sz["ff_e"]}, "shared": {"ff": 2 * sz["ff_e"]},
+           "router": {"experts": sz["experts"], "identity": 4, "top": sz["top"], "groups": {"count": 4, "keep": 3}}}
+    dense = {"kind": "dense", "ff": sz["ff"], "limit": 7.0}
+    layers = []
+    for i in range(sz["layers"]):
+        mx = dict(att)
+        if i % 2 == 1:
+            mx["kv_from"] = i - 1
+        layers.append({"type": "attention", "mixer": mx, "mlp": moe if i % 2 == 1 else dense})
+    return {"architecture": "Dizizen", "vocab": sz["vocab"], "width": sz["width"], "layers": layers, "norm": {"eps": 1e-5},
+            "embedding": {"scale": 1.0}, "residual_mult": 0.5}
+
+
+def _dizizen_params(sz, rows):
+    """(Linear parameters one token uses at most (every choice a real expert), parameters a step of `rows` tokens reads,
+    cache bytes per cached position)."""
+    D, H, d = sz["width"], sz["heads"], sz["dim"]
+    E, top, fe, F = sz["experts"], sz["top"], sz["ff_e"], sz["ff"]
+    slots = E + 4
+    touched = E * (1.0 - (1.0 - top / slots) ** rows)   # expected number of distinct experts a step reads
+    active = read = cache = 0
+    for i in range(sz["layers"]):
+        own = i % 2 == 0
+        mix = D * (H * d + (2 * 8 * d if own else 0)) + H * d * D + D * D
+        if own:
+            cache += 2 * 8 * d * 2
+            ff_a = ff_r = D * D + 3 * D * F
+        else:
+            ff_a = D * D + slots * D + top * 2 * D * fe + 2 * D * 2 * fe
+            ff_r = D * D + slots * D + touched * 2 * D * fe + 2 * D * 2 * fe
+        active += mix + ff_a
+        read += mix + ff_r
+    return active + sz["vocab"] * D, read + sz["vocab"] * D, cache
+
+
+def run_compare_dizizen(args):
+    import numpy as np
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    torch.cuda.set_device(0)
+    from zhilight_b200 import build
+    build.build()
+    from zhilight_b200.dizizen import DizizenDecoder
+    from zhilight_b200.kodupel import KodupelDecoder
+    hbm, how = read_peaks()
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    tflops = json.load(open(peaks_path))["bf16_tflops"] if os.path.exists(peaks_path) else 1590.0
+    ctx, chunk, n_prompt = args.prompt if args.prompt > 128 else 1024, 1024, 2048
+    steps, warm = max(args.steps, 16), max(args.warmup, 3)
+    rng = np.random.default_rng(0)
+    rows = []
+    sampler = ClockSampler(0)
+    sampler.start()
+    sampler.mark_region_start()
+    for name, sz in KODUPEL_SIZES.items():
+        if args.compare_sizes and name not in args.compare_sizes.split(","):
+            continue
+        for kind in [k for k in ("dizizen", "kodupel") if k in args.compare_models.split(",")]:
+            max_seq = max(ctx, n_prompt) + 4 * (steps + warm) + 64
+            kw = dict(dtype="bf16", max_batch=32, max_seq=max_seq, max_step_tokens=chunk, use_pdl=not args.no_pdl,
+                      use_graph=not args.no_graph)
+            if kind == "dizizen":
+                dec = DizizenDecoder.from_config_dict(_dizizen_config(sz), **kw)
+            else:
+                dec = KodupelDecoder.from_config_dict(_kodupel_config(sz), **kw)
+            dec.init_synthetic(seed=1)
+            stream = torch.cuda.ExternalStream(dec.stream())
+            out = {"size": name, "model": kind}
+            toks = rng.integers(0, sz["vocab"], n_prompt).astype(np.int32)
+            for _ in range(2):
+                dec.prefill(0, toks, 0)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(3):
+                dec.prefill(0, toks, 0)
+            e1.record(stream)
+            e1.synchronize()
+            ms = e0.elapsed_time(e1) / 3
+            active = _dizizen_params(sz, 1)[0] if kind == "dizizen" else _kodupel_params(sz, 1)[0]
+            out["linear_params_per_token"] = int(active)
+            flops = 2.0 * (active - sz["vocab"] * sz["width"]) * n_prompt
+            out["prefill"] = {"tokens": n_prompt, "chunk": chunk, "ms": round(ms, 3), "tok_s": round(n_prompt / ms * 1e3),
+                              "linear_tflops": round(flops / ms / 1e9, 1),
+                              "of_measured_bf16_peak": round(flops / ms / 1e9 / tflops, 4)}
+            for b in range(32):
+                dec.prefill(b, toks[:ctx], 0)
+            for B in (1, 32):
+                dec.set_state(rng.integers(0, sz["vocab"], B).astype(np.int32), np.full(B, ctx, dtype=np.int32))
+                ms, _ = measure_decode(dec, B, steps, warm, stream, torch.cuda.synchronize)
+                mid = ctx + warm + steps // 2
+                if kind == "dizizen":
+                    _, read, cache = _dizizen_params(sz, B)
+                    step_bytes = read * 2 + B * mid * cache
+                else:
+                    _, read, cache, state = _kodupel_params(sz, B)
+                    step_bytes = read * 2 + B * (mid * cache + state)
+                out["decode_b%d" % B] = {"ctx": ctx, "ms_per_step": round(ms / steps, 4), "tok_s": round(B * steps / ms * 1e3, 1),
+                                          "step_bytes": int(step_bytes),
+                                          "of_%s_hbm_peak" % how: round(step_bytes / (ms / steps * 1e-3) / 1e9 / hbm, 4)}
+            out["kernels_per_step"] = dec.stats()[1]
+            dec.close()
+            del dec
+            torch.cuda.empty_cache()
+            rows.append(out)
+            print(json.dumps(out), file=sys.stderr, flush=True)
+    clocks = sampler.finish()
+    print(json.dumps({"compare": "dizizen vs kodupel (bf16, random weights, synthetic tokens)", "rows": rows, "clocks": clocks,
+                      "timing": "CUDA events on the model's stream; weights per pass larger than L2"}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -715,11 +837,18 @@ def main():
                     help="instead of the default workload: Kodupel beside the bf16 Llama decoder at a few layer sizes")
     ap.add_argument("--compare-lagelorn", action="store_true",
                     help="instead of the default workload: Lagelorn beside Kodupel at a few layer sizes")
+    ap.add_argument("--compare-dizizen", action="store_true",
+                    help="instead of the default workload: Dizizen beside Kodupel at a few layer sizes")
     ap.add_argument("--compare-dekipel", action="store_true",
                     help="instead of the default workload: Dekipel beside the bf16 Llama decoder at a few layer sizes")
     args = ap.parse_args()
     if args.compare_dekipel:
         run_compare_dekipel(args)
+        return
+    if args.compare_dizizen:
+        if args.compare_models == "dekipel,llama":
+            args.compare_models = "dizizen,kodupel"
+        run_compare_dizizen(args)
         return
     if args.compare_lagelorn:
         if args.compare_models == "dekipel,llama":

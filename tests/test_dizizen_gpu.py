@@ -287,14 +287,17 @@ def test_router_groups_identity_slots_and_weights(cuda, lib):
     assert (np.sort(te1, axis=1) == np.arange(S)).all()
 
 
-@pytest.mark.parametrize("D", [40, 300])
-def test_gated_parallel_combine(cuda, lib, D):
+@pytest.mark.parametrize("aligned", [True, False])
+@pytest.mark.parametrize("D", [40, 300, 4100])
+def test_gated_parallel_combine(cuda, lib, D, aligned):
+    """aligned rows of a width up to 4096 take the kernel's register path, the others the channel-by-channel one."""
     import torch
     from zhilight_b200 import ops
     rng = np.random.default_rng(4)
     T, P, n_real, eps, mult = 9, 3, 5, 1e-5, 0.6
+    ga, gf, wide = (4, D + 8, 2 * D + 12) if aligned else (3, D + 5, 2 * D + 7)
     x = rng.standard_normal((T, D)).astype(np.float32)
-    gates = rng.standard_normal((T, 2 * D + 7)).astype(np.float32)
+    gates = rng.standard_normal((T, wide)).astype(np.float32)
     a, fd = rng.standard_normal((T, D)).astype(np.float32), rng.standard_normal((T, D)).astype(np.float32)
     parts = rng.standard_normal((T, P, D)).astype(np.float32)
     coef = rng.random((T, P)).astype(np.float32)
@@ -307,26 +310,28 @@ def test_gated_parallel_combine(cuda, lib, D):
     for t in range(T):
         for p in range(P):
             f[t] += coef[t, p] * (parts[t, p] if choice[t, p] < n_real else h[t])
-    g1, g2 = orc.sigmoid(gates[:, 3:3 + D].astype(np.float64)), orc.sigmoid(gates[:, 5 + D:5 + 2 * D].astype(np.float64))
+    g1, g2 = orc.sigmoid(gates[:, ga:ga + D].astype(np.float64)), orc.sigmoid(gates[:, gf:gf + D].astype(np.float64))
     want = x + mult * (sa * g1 * a + sf * g2 * f)
     xd = dev(x, cuda)
-    hn = ops.gated_parallel_combine(xd, mult, dev(gates, cuda), 3, dev(a, cuda), dev(sa, cuda), eps, parts=dev(parts, cuda),
+    hn = ops.gated_parallel_combine(xd, mult, dev(gates, cuda), ga, dev(a, cuda), dev(sa, cuda), eps, parts=dev(parts, cuda),
                                     coef=dev(coef, cuda), choice=dev(choice, cuda), n_real=n_real, f_dense=dev(fd, cuda),
-                                    gf_off=5 + D, scale_f=dev(sf, cuda), norm_w=dev(nw, cuda), next_w=dev(nxt, cuda),
+                                    gf_off=gf, scale_f=dev(sf, cuda), norm_w=dev(nw, cuda), next_w=dev(nxt, cuda),
                                     act_dtype=torch.bfloat16)
-    assert np.abs(xd.cpu().numpy() - want).max() < 2e-5
-    assert np.abs(hn.float().cpu().numpy() - orc.zero_centred_norm(want, nxt.astype(np.float64) - 1.0, eps)).max() < 3e-2
+    assert np.abs(xd.cpu().numpy() - want).max() < 3e-6 * np.abs(want).max()
+    ref = orc.zero_centred_norm(want, nxt.astype(np.float64) - 1.0, eps)
+    assert np.abs(hn.float().cpu().numpy() - ref).max() < 2.0 ** -8 * np.abs(ref).max()      # one bfloat16 rounding
     # no second sublayer, no next norm
     xd = dev(x, cuda)
-    assert ops.gated_parallel_combine(xd, mult, dev(gates, cuda), 3, dev(a, cuda), dev(sa, cuda), eps) is None
-    assert np.abs(xd.cpu().numpy() - (x + mult * sa * g1 * a)).max() < 2e-5
+    assert ops.gated_parallel_combine(xd, mult, dev(gates, cuda), ga, dev(a, cuda), dev(sa, cuda), eps) is None
+    assert np.abs(xd.cpu().numpy() - (x + mult * sa * g1 * a)).max() < 3e-6 * np.abs(want).max()
     # only a dense second sublayer, float32 next norm
     xd = dev(x, cuda)
-    hn = ops.gated_parallel_combine(xd, mult, dev(gates, cuda), 3, dev(a, cuda), dev(sa, cuda), eps, f_dense=dev(fd, cuda),
-                                    gf_off=5 + D, scale_f=dev(sf, cuda), next_w=dev(nxt, cuda))
+    hn = ops.gated_parallel_combine(xd, mult, dev(gates, cuda), ga, dev(a, cuda), dev(sa, cuda), eps, f_dense=dev(fd, cuda),
+                                    gf_off=gf, scale_f=dev(sf, cuda), next_w=dev(nxt, cuda))
     want = x + mult * (sa * g1 * a + sf * g2 * fd)
-    assert np.abs(xd.cpu().numpy() - want).max() < 2e-5
-    assert np.abs(hn.cpu().numpy() - orc.zero_centred_norm(want, nxt.astype(np.float64) - 1.0, eps)).max() < 2e-5
+    assert np.abs(xd.cpu().numpy() - want).max() < 3e-6 * np.abs(want).max()
+    ref = orc.zero_centred_norm(want, nxt.astype(np.float64) - 1.0, eps)
+    assert np.abs(hn.cpu().numpy() - ref).max() < 3e-6 * np.abs(ref).max()
 
 
 # ---------------------------------------------------------------------------------------------- the whole model

@@ -2,7 +2,7 @@
 // Same driver shape as kodupel_runner.cu (task slots, host (token, slot, position) rows in, logits / greedy picks out),
 // built from the shared pieces of runner_common.cuh.
 //
-// x = scale * embed[token] in fp32.  A layer is parallel: h = norm1(x) (weight 1 + w) feeds both sublayers and
+// x = scale * embed[token] in fp32 (the embedding kernel also writes the first layer's normed input).  A layer is parallel: h = norm1(x) (weight 1 + w) feeds both sublayers and
 //   x += mult * (ls1 * sigmoid(W_rg1 h + b) * mixer(h) + ls2 * sigmoid(W_rg2 h + b) * ff(h)).
 // Everything that is a Linear of h without an activation is ONE projection [W_q; W_k; W_v; W_rg1; W_rg2; W_router] with one
 // bias vector and fp32 output: the attention operands, both gates' logits and the router's logits are columns of it.
@@ -110,6 +110,46 @@ int rot_index(zl_dizizen* m, double base, int dims) {
     r.dims = dims;
     m->rots.push_back(r);
     return (int)m->rots.size() - 1;
+}
+
+// x[t] = scale * embed[token[t]] in fp32 and the first layer's input h[t] = w * x[t] / sqrt(mean(x[t]^2) + eps) in the
+// activation dtype; one CTA per token, the row in registers for widths up to 8 * 256
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(256) k_embed_scaled_norm(const int32_t* __restrict__ ids, const TW* __restrict__ table,
+                                                           const float* __restrict__ w, float* __restrict__ x, TO* __restrict__ h,
+                                                           int D, int vocab, float scale, float eps) {
+    __shared__ float red[8];
+    int id = ids[blockIdx.x];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    const TW* src = table + (size_t)id * D;
+    float* xr = x + (size_t)blockIdx.x * D;
+    float keep[8], ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int c = threadIdx.x + i * 256;
+        keep[i] = c < D ? to_f32<TW>(src[c]) * scale : 0.f;
+        if (c < D) xr[c] = keep[i];
+        ss = fmaf(keep[i], keep[i], ss);
+    }
+    for (int c = threadIdx.x + 2048; c < D; c += 256) {
+        const float v = to_f32<TW>(src[c]) * scale;
+        xr[c] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float r = 1.0f / sqrtf(tot / (float)D + eps);
+    TO* hr = h + (size_t)blockIdx.x * D;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int c = threadIdx.x + i * 256;
+        if (c < D) hr[c] = from_f32<TO>(keep[i] * r * w[c]);
+    }
+    for (int c = threadIdx.x + 2048; c < D; c += 256) hr[c] = from_f32<TO>(xr[c] * r * w[c]);
 }
 
 int finalize_ff(zl_dizizen* m, int l) {
@@ -295,13 +335,14 @@ int enqueue_step(zl_dizizen* m, int T, int n_want, int n_runs, int max_run, int 
     cudaStream_t st = m->stream;
     const int pg = pdl_for(m, 2, T), pr = pdl_for(m, 4, T), pa = pdl_for(m, 8, T), pt = pdl_for(m, 32, T);
     if (dt == ZL_F32)
-        ZL_CHECK_CUDA(launch(k_embed_f32<float>, dim3(T), dim3(128), 0, st, false, (const int32_t*)m->d_tokens,
-                             (const float*)m->embed, m->x, D, c.vocab, c.embed_scale));
+        ZL_CHECK_CUDA(launch(k_embed_scaled_norm<float, float>, dim3(T), dim3(256), 0, st, false, (const int32_t*)m->d_tokens,
+                             (const float*)m->embed, (const float*)m->layers[0].norm1, m->x, (float*)m->h, D, c.vocab,
+                             c.embed_scale, c.eps));
     else
-        ZL_CHECK_CUDA(launch(k_embed_f32<__nv_bfloat16>, dim3(T), dim3(128), 0, st, false, (const int32_t*)m->d_tokens,
-                             (const __nv_bfloat16*)m->embed, m->x, D, c.vocab, c.embed_scale));
+        ZL_CHECK_CUDA(launch(k_embed_scaled_norm<__nv_bfloat16, __nv_bfloat16>, dim3(T), dim3(256), 0, st, false,
+                             (const int32_t*)m->d_tokens, (const __nv_bfloat16*)m->embed, (const float*)m->layers[0].norm1, m->x,
+                             (__nv_bfloat16*)m->h, D, c.vocab, c.embed_scale, c.eps));
     for (auto& r : m->rots) RCHECK(zl_rope_table(m->d_pos, T, r.inv_freq, r.dims / 2, r.table, pr, st));
-    RCHECK(zl_group_rmsnorm(m->x, D, m->layers[0].norm1, m->h, D, T, D, 1, c.eps, dt, pr, st));
     for (int l = 0; l < c.num_layers; ++l) {
         DLayer& L = m->layers[l];
         const auto& lc = L.c;

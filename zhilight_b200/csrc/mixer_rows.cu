@@ -453,11 +453,25 @@ __device__ __forceinline__ float block_sum_256(float v, float* red) {
     return tot;
 }
 
+__device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf(-v)); }
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <typename TO>
+__device__ __forceinline__ void store4(TO* dst, float a, float b, float c, float d) {
+    if constexpr (sizeof(TO) == 4) {
+        *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+    } else {
+        TO v[4] = {from_f32<TO>(a), from_f32<TO>(b), from_f32<TO>(c), from_f32<TO>(d)};
+        *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(v);
+    }
+}
+
 // x[t] += mult * (scale_a sigmoid(g_a) a[t] + scale_f sigmoid(g_f) f[t]), f[t] = sum_p coef_p * (part_p or the sublayers'
 // input norm_w * rms(x_old)) + f_dense[t], the parts added in the order of p; then the next layer's norm of the new x.
-// One CTA per token; dynamic shared memory D floats (the new x between the two passes).
+// One CTA per token.  vec (D % 4 == 0, D <= 4096, every row 16-byte aligned): a thread keeps its (up to four) 4-channel
+// pieces of x in registers and every load of a piece is independent of the others; otherwise channel by channel with the
+// new x in dynamic shared memory (D floats) between the two passes.
 template <typename TO>
-__global__ void __launch_bounds__(256) k_gated_parallel_combine(GatedCombineP p) {
+__global__ void __launch_bounds__(256) k_gated_parallel_combine(GatedCombineP p, int vec) {
     extern __shared__ float gsx[];
     __shared__ float red[8];
     pdl_trigger();
@@ -465,22 +479,83 @@ __global__ void __launch_bounds__(256) k_gated_parallel_combine(GatedCombineP p)
     const int t = blockIdx.x, D = p.D;
     float* xr = p.x + (size_t)t * p.ldx;
     const float* gr = p.gates + (size_t)t * p.ldg;
+    const float* ar = p.a + (size_t)t * p.lda;
     const bool second = p.parts || p.f_dense;
     const int32_t* ch = p.choice ? p.choice + (size_t)t * p.n_parts : nullptr;
     const float* cf = p.coef ? p.coef + (size_t)t * p.n_parts : nullptr;
     bool through = false;
     if (p.parts && ch)
         for (int q = 0; q < p.n_parts; ++q) through |= ch[q] >= p.n_real;
+    TO* h = p.next_w ? static_cast<TO*>(p.h_next) + (size_t)t * D : nullptr;
+    if (vec) {
+        float4 xv[4];
+        float so = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = (threadIdx.x + i * 256) * 4;
+            xv[i] = c < D ? ld4(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            so = fmaf(xv[i].x, xv[i].x, fmaf(xv[i].y, xv[i].y, fmaf(xv[i].z, xv[i].z, fmaf(xv[i].w, xv[i].w, so))));
+        }
+        float r_old = 0.f;
+        if (through) r_old = 1.0f / sqrtf(block_sum_256(so, red) / (float)D + p.eps);   // uniform over the CTA
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = (threadIdx.x + i * 256) * 4;
+            if (c >= D) continue;
+            const float4 sa = ld4(p.scale_a + c), ga = ld4(gr + p.ga_off + c), av = ld4(ar + c);
+            float4 s = make_float4(sa.x * sigmoid_f(ga.x) * av.x, sa.y * sigmoid_f(ga.y) * av.y, sa.z * sigmoid_f(ga.z) * av.z,
+                                   sa.w * sigmoid_f(ga.w) * av.w);
+            if (second) {
+                const float4 sf = ld4(p.scale_f + c), gf = ld4(gr + p.gf_off + c);
+                float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (p.parts) {
+                    float4 hv = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (through) {
+                        const float4 nw = ld4(p.norm_w + c);
+                        hv = make_float4(xv[i].x * r_old * nw.x, xv[i].y * r_old * nw.y, xv[i].z * r_old * nw.z, xv[i].w * r_old * nw.w);
+                    }
+#pragma unroll 4
+                    for (int q = 0; q < p.n_parts; ++q) {
+                        const float4 v = (ch && ch[q] >= p.n_real) ? hv : ld4(p.parts + ((size_t)t * p.n_parts + q) * p.ldp + c);
+                        const float w = cf ? cf[q] : 1.0f;
+                        f.x = fmaf(w, v.x, f.x), f.y = fmaf(w, v.y, f.y), f.z = fmaf(w, v.z, f.z), f.w = fmaf(w, v.w, f.w);
+                    }
+                }
+                if (p.f_dense) {
+                    const float4 fd = ld4(p.f_dense + (size_t)t * p.ldf + c);
+                    f.x += fd.x, f.y += fd.y, f.z += fd.z, f.w += fd.w;
+                }
+                s.x = fmaf(sf.x * sigmoid_f(gf.x), f.x, s.x), s.y = fmaf(sf.y * sigmoid_f(gf.y), f.y, s.y);
+                s.z = fmaf(sf.z * sigmoid_f(gf.z), f.z, s.z), s.w = fmaf(sf.w * sigmoid_f(gf.w), f.w, s.w);
+            }
+            const float4 nx = make_float4(fmaf(p.mult, s.x, xv[i].x), fmaf(p.mult, s.y, xv[i].y), fmaf(p.mult, s.z, xv[i].z),
+                                          fmaf(p.mult, s.w, xv[i].w));
+            *reinterpret_cast<float4*>(xr + c) = nx;
+            xv[i] = nx;
+            ss = fmaf(nx.x, nx.x, fmaf(nx.y, nx.y, fmaf(nx.z, nx.z, fmaf(nx.w, nx.w, ss))));
+        }
+        if (!h) return;
+        const float r = 1.0f / sqrtf(block_sum_256(ss, red) / (float)D + p.eps);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = (threadIdx.x + i * 256) * 4;
+            if (c >= D) continue;
+            const float4 nw = ld4(p.next_w + c);
+            store4<TO>(h + c, xv[i].x * r * nw.x, xv[i].y * r * nw.y, xv[i].z * r * nw.z, xv[i].w * r * nw.w);
+        }
+        return;
+    }
     float r_old = 0.f;
     if (through) {   // uniform over the CTA
-        float ss = 0.f;
-        for (int c = threadIdx.x; c < D; c += 256) ss = fmaf(xr[c], xr[c], ss);
-        r_old = 1.0f / sqrtf(block_sum_256(ss, red) / (float)D + p.eps);
+        float so = 0.f;
+        for (int c = threadIdx.x; c < D; c += 256) so = fmaf(xr[c], xr[c], so);
+        r_old = 1.0f / sqrtf(block_sum_256(so, red) / (float)D + p.eps);
     }
     float ss = 0.f;
     for (int c = threadIdx.x; c < D; c += 256) {
         const float xv = xr[c];
-        float s = p.scale_a[c] * (1.0f / (1.0f + expf(-gr[p.ga_off + c]))) * p.a[(size_t)t * p.lda + c];
+        float s = p.scale_a[c] * sigmoid_f(gr[p.ga_off + c]) * ar[c];
         if (second) {
             float f = 0.f;
             if (p.parts)
@@ -489,16 +564,15 @@ __global__ void __launch_bounds__(256) k_gated_parallel_combine(GatedCombineP p)
                     f = fmaf(cf ? cf[q] : 1.0f, v, f);
                 }
             if (p.f_dense) f += p.f_dense[(size_t)t * p.ldf + c];
-            s = fmaf(p.scale_f[c] * (1.0f / (1.0f + expf(-gr[p.gf_off + c]))), f, s);
+            s = fmaf(p.scale_f[c] * sigmoid_f(gr[p.gf_off + c]), f, s);
         }
         const float nx = fmaf(p.mult, s, xv);
         xr[c] = nx;
         gsx[c] = nx;
         ss = fmaf(nx, nx, ss);
     }
-    if (!p.next_w) return;
+    if (!h) return;
     const float r = 1.0f / sqrtf(block_sum_256(ss, red) / (float)D + p.eps);
-    TO* h = static_cast<TO*>(p.h_next) + (size_t)t * D;
     for (int c = threadIdx.x; c < D; c += 256) h[c] = from_f32<TO>(gsx[c] * r * p.next_w[c]);
 }
 
@@ -548,7 +622,13 @@ extern "C" int zl_gated_parallel_combine(float* x, long long ldx, float mult, co
     ZL_CHECK_ARG(!next_w || (h_next && (act_dtype == ZL_F16 || act_dtype == ZL_BF16 || act_dtype == ZL_F32)));
     GatedCombineP p{x, ldx, mult, gates, ldg, a, lda, ga_off, scale_a, parts, ldp, coef, choice, n_parts, n_real, f_dense, ldf,
                     gf_off, scale_f, norm_w, next_w, h_next, D, eps};
-    const size_t smem = (size_t)D * sizeof(float);
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    const int vec = D % 4 == 0 && D <= 4096 && ldx % 4 == 0 && ldg % 4 == 0 && lda % 4 == 0 && ga_off % 4 == 0 && al16(x) &&
+                    al16(gates) && al16(a) && al16(scale_a) &&
+                    (!(parts || f_dense) || (gf_off % 4 == 0 && al16(scale_f))) &&
+                    (!parts || (ldp % 4 == 0 && al16(parts) && (!choice || al16(norm_w)))) &&
+                    (!f_dense || (ldf % 4 == 0 && al16(f_dense))) && (!next_w || (al16(next_w) && al16(h_next)));
+    const size_t smem = vec ? 0 : (size_t)D * sizeof(float);
     ZL_CHECK_SUPPORTED(smem <= 200 * 1024);
     cudaError_t e = cudaSuccess;
     static size_t set_for[3] = {0, 0, 0};
@@ -560,9 +640,9 @@ extern "C" int zl_gated_parallel_combine(float* x, long long ldx, float mult, co
         ZL_CHECK_CUDA(e);
         set_for[ti] = smem;
     }
-    if (ti == 0) e = launch(k_gated_parallel_combine<float>, dim3(T), dim3(256), smem, stream, pdl != 0, p);
-    else if (ti == 1) e = launch(k_gated_parallel_combine<__nv_bfloat16>, dim3(T), dim3(256), smem, stream, pdl != 0, p);
-    else e = launch(k_gated_parallel_combine<__half>, dim3(T), dim3(256), smem, stream, pdl != 0, p);
+    if (ti == 0) e = launch(k_gated_parallel_combine<float>, dim3(T), dim3(256), smem, stream, pdl != 0, p, vec);
+    else if (ti == 1) e = launch(k_gated_parallel_combine<__nv_bfloat16>, dim3(T), dim3(256), smem, stream, pdl != 0, p, vec);
+    else e = launch(k_gated_parallel_combine<__half>, dim3(T), dim3(256), smem, stream, pdl != 0, p, vec);
     ZL_CHECK_CUDA(e);
     return ZL_OK;
 }

@@ -183,7 +183,8 @@ extern "C" int zl_moe_route_grouped(const float* x, long long ldx, const float* 
     ZL_CHECK_ARG(w_router || ldx >= slots);
     ZL_CHECK_ARG(groups >= 1 && slots % groups == 0 && keep >= 1 && keep <= groups && keep * (slots / groups) >= top);
     ZL_CHECK_ARG(score_fn == ZL_MOE_SCORE_SIGMOID || score_fn == ZL_MOE_SCORE_SOFTMAX);
-    ZL_CHECK_CUDA(launch(k_moe_route, dim3(T), dim3(kRouteWarps * 32), (size_t)(2 * slots + groups) * sizeof(float), stream,
+    // with ready logits only the choosing warp has work
+    ZL_CHECK_CUDA(launch(k_moe_route, dim3(T), dim3(w_router ? kRouteWarps * 32 : 32), (size_t)(2 * slots + groups) * sizeof(float), stream,
                          pdl != 0, x, ldx, w_router, correction, top_experts, top_weights, D, slots, top, score_fn, renormalize,
                          groups, keep, renorm_eps));
     ZL_CHECK_CUDA(launch(k_moe_plan, dim3(1), dim3(1024), (size_t)2 * (slots + 1) * sizeof(int), stream, pdl != 0,
