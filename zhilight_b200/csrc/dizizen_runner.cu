@@ -69,6 +69,8 @@ struct RotTable {
 struct zl_dizizen {
     zl_dizizen_config_t cfg{};
     cudaStream_t stream = nullptr;
+    cudaStream_t side = nullptr;                 // the feed-forward branch of a layer runs here beside the mixer
+    std::vector<cudaEvent_t> ev_h, ev_proj, ev_ff;   // per layer: h ready, projection ready (main) / feed-forward done (side)
     StagedMap staged;
     std::vector<DLayer> layers;
     std::vector<RotTable> rots;
@@ -320,13 +322,13 @@ int pdl_mask() {
 int pdl_for(const zl_dizizen* m, int bit, int T) { return (m->cfg.use_pdl && T <= 8 && (pdl_mask() & bit)) ? 1 : 0; }
 
 // y (M, N) = x (M, K) @ w (N, K)^T + bias, optional relu^2.  bias_f32 / bias_act are the same numbers in two types.
-int linear(zl_dizizen* m, const void* x, int K, const void* w, int N, const float* bias_f32, const void* bias_act, void* y,
-           int M, int out_dtype, int epi) {
+int linear(zl_dizizen* m, cudaStream_t st, const void* x, int K, const void* w, int N, const float* bias_f32,
+           const void* bias_act, void* y, int M, int out_dtype, int epi) {
     const auto& c = m->cfg;
     if (c.dtype != ZL_F32 && epi == ZL_GEMM_EPI_NONE && M <= 32 && K % 32 == 0 && N >= 64 && (!bias_f32 || bias_act) &&
         (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0)
-        return zl_dense_gemm_skinny_act(x, K, w, bias_act, y, M, N, K, c.dtype, out_dtype, 0, pdl_for(m, 1, M), m->stream);
-    return zl_gemm_nt_bias(x, K, w, K, bias_f32, y, N, M, N, K, c.dtype, out_dtype, epi, pdl_for(m, 2, M), m->stream);
+        return zl_dense_gemm_skinny_act(x, K, w, bias_act, y, M, N, K, c.dtype, out_dtype, 0, pdl_for(m, 1, M), st);
+    return zl_gemm_nt_bias(x, K, w, K, bias_f32, y, N, M, N, K, c.dtype, out_dtype, epi, pdl_for(m, 2, M), st);
 }
 
 int enqueue_step(zl_dizizen* m, int T, int n_want, int n_runs, int max_run, int max_len) {
@@ -343,43 +345,60 @@ int enqueue_step(zl_dizizen* m, int T, int n_want, int n_runs, int max_run, int 
                              (const int32_t*)m->d_tokens, (const __nv_bfloat16*)m->embed, (const float*)m->layers[0].norm1, m->x,
                              (__nv_bfloat16*)m->h, D, c.vocab, c.embed_scale, c.eps));
     for (auto& r : m->rots) RCHECK(zl_rope_table(m->d_pos, T, r.inv_freq, r.dims / 2, r.table, pr, st));
+    // The two sublayers of a layer read the same h and meet only in the combine kernel: the feed-forward runs on a second
+    // stream beside the mixer (fork after h, join before the combine; inside a captured step the events become graph edges).
+    // A routed feed-forward needs the projection's logit columns, its shared expert does not.  ZL_DIZIZEN_ONE_STREAM=1: all
+    // kernels on one stream in the order mixer, feed-forward.
+    static const bool one_stream = getenv("ZL_DIZIZEN_ONE_STREAM") != nullptr;
     for (int l = 0; l < c.num_layers; ++l) {
         DLayer& L = m->layers[l];
         const auto& lc = L.c;
         const int H = lc.heads;
-        RCHECK(linear(m, m->h, D, L.w_in, L.n_in, L.b_in, L.b_in_act, m->proj, T, ZL_F32, ZL_GEMM_EPI_NONE));
+        const bool fork = !one_stream && lc.ff_kind != ZL_FF_NONE;
+        cudaStream_t sf = fork ? m->side : st;
+        if (fork) {
+            ZL_CHECK_CUDA(cudaEventRecord(m->ev_h[l], st));
+            ZL_CHECK_CUDA(cudaStreamWaitEvent(sf, m->ev_h[l], 0));
+        }
+        RCHECK(linear(m, st, m->h, D, L.w_in, L.n_in, L.b_in, L.b_in_act, m->proj, T, ZL_F32, ZL_GEMM_EPI_NONE));
+        if (fork && lc.ff_kind == ZL_FF_MOE) ZL_CHECK_CUDA(cudaEventRecord(m->ev_proj[l], st));
         const float* vtab = m->rots[L.v_rot].table;
         RCHECK(zl_qkv_table_rope_append(m->proj, L.n_in, L.q_off, L.k_off, L.v_off, H, lc.kv_heads, lc.dim, lc.vdim,
-                                  L.qk_rot >= 0 ? m->rots[L.qk_rot].table : nullptr, lc.rot_dims, vtab, ZL_ROT_HALVES, m->q,
-                                  L.k_addrs, L.v_addrs, m->d_slots, m->d_pos, T, dt, pr, st));
+                                        L.qk_rot >= 0 ? m->rots[L.qk_rot].table : nullptr, lc.rot_dims, vtab, ZL_ROT_HALVES, m->q,
+                                        L.k_addrs, L.v_addrs, m->d_slots, m->d_pos, T, dt, pr, st));
         const int splits = zl_sink_attention_splits(T, H, lc.kv_heads, max_len);
         RCHECK(zl_sink_attention_ex(m->q, L.k_addrs, L.v_addrs, m->d_slots, m->d_pos, nullptr, 1, nullptr, 0, lc.scale, 0, nullptr,
                                     0, vtab, ZL_ROT_HALVES, m->att, T, H, lc.kv_heads, lc.dim, lc.vdim, splits, m->attn_ws,
                                     m->attn_ws_bytes, m->d_run0, m->d_runlen, n_runs, max_run, dt, pa, st));
-        RCHECK(linear(m, m->att, H * lc.vdim, L.o, D, L.o_b, L.o_b_act, m->ya, T, ZL_F32, ZL_GEMM_EPI_NONE));
+        RCHECK(linear(m, st, m->att, H * lc.vdim, L.o, D, L.o_b, L.o_b_act, m->ya, T, ZL_F32, ZL_GEMM_EPI_NONE));
         const float *parts = nullptr, *f_dense = nullptr;
         if (lc.ff_kind == ZL_FF_DENSE) {
             RCHECK(zl_gemm_nt_glu_clamp(m->h, D, L.w_gu, D, L.b_gu, m->act, lc.ff, T, 2 * lc.ff, D, dt, dt, lc.limit, 1.702f, 1.0f,
-                                        pg, st));
-            RCHECK(linear(m, m->act, lc.ff, L.w_down, D, L.b_down, L.b_down_act, m->yf, T, ZL_F32, ZL_GEMM_EPI_NONE));
+                                        pg, sf));
+            RCHECK(linear(m, sf, m->act, lc.ff, L.w_down, D, L.b_down, L.b_down_act, m->yf, T, ZL_F32, ZL_GEMM_EPI_NONE));
             f_dense = m->yf;
         } else if (lc.ff_kind == ZL_FF_MOE) {
             const int E = lc.experts, F = lc.ff;
-            RCHECK(zl_moe_route_grouped(m->proj + L.r_off, L.n_in, nullptr, L.correction, m->top_e, m->top_w, m->grp_off,
-                                        m->list_token, m->list_pair, T, D, E + lc.identity, lc.top, lc.groups, lc.keep,
-                                        ZL_MOE_SCORE_SOFTMAX, 1, 1e-20f, pr, st));
-            if (E > 0) {
-                RCHECK(zl_gemm_nt_grouped(m->h, D, m->list_token, L.w_up, D, (long long)F * D, m->act, F, nullptr, m->grp_off, E,
-                                          T, F, D, dt, dt, ZL_GEMM_EPI_RELU2, 0.f, 1.f, 0.f, pg, st));
-                RCHECK(zl_gemm_nt_grouped(m->act, F, nullptr, L.w_down, F, (long long)D * F, m->ypair, D, m->list_pair,
-                                          m->grp_off, E, T, D, F, dt, ZL_F32, ZL_GEMM_EPI_NONE, 0.f, 1.f, 0.f, pg, st));
-            }
-            parts = m->ypair;
             if (lc.shared_ff > 0) {
-                RCHECK(linear(m, m->h, D, L.s_up, lc.shared_ff, nullptr, nullptr, m->act_s, T, dt, ZL_GEMM_EPI_RELU2));
-                RCHECK(linear(m, m->act_s, lc.shared_ff, L.s_down, D, nullptr, nullptr, m->yf, T, ZL_F32, ZL_GEMM_EPI_NONE));
+                RCHECK(linear(m, sf, m->h, D, L.s_up, lc.shared_ff, nullptr, nullptr, m->act_s, T, dt, ZL_GEMM_EPI_RELU2));
+                RCHECK(linear(m, sf, m->act_s, lc.shared_ff, L.s_down, D, nullptr, nullptr, m->yf, T, ZL_F32, ZL_GEMM_EPI_NONE));
                 f_dense = m->yf;
             }
+            if (fork) ZL_CHECK_CUDA(cudaStreamWaitEvent(sf, m->ev_proj[l], 0));
+            RCHECK(zl_moe_route_grouped(m->proj + L.r_off, L.n_in, nullptr, L.correction, m->top_e, m->top_w, m->grp_off,
+                                        m->list_token, m->list_pair, T, D, E + lc.identity, lc.top, lc.groups, lc.keep,
+                                        ZL_MOE_SCORE_SOFTMAX, 1, 1e-20f, pr, sf));
+            if (E > 0) {
+                RCHECK(zl_gemm_nt_grouped(m->h, D, m->list_token, L.w_up, D, (long long)F * D, m->act, F, nullptr, m->grp_off, E,
+                                          T, F, D, dt, dt, ZL_GEMM_EPI_RELU2, 0.f, 1.f, 0.f, pg, sf));
+                RCHECK(zl_gemm_nt_grouped(m->act, F, nullptr, L.w_down, F, (long long)D * F, m->ypair, D, m->list_pair,
+                                          m->grp_off, E, T, D, F, dt, ZL_F32, ZL_GEMM_EPI_NONE, 0.f, 1.f, 0.f, pg, sf));
+            }
+            parts = m->ypair;
+        }
+        if (fork) {
+            ZL_CHECK_CUDA(cudaEventRecord(m->ev_ff[l], sf));
+            ZL_CHECK_CUDA(cudaStreamWaitEvent(st, m->ev_ff[l], 0));
         }
         const float* next_w = l + 1 < c.num_layers ? m->layers[l + 1].norm1 : nullptr;
         RCHECK(zl_gated_parallel_combine(m->x, D, c.residual_mult, m->proj, L.n_in, m->ya, D, L.g1_off, L.ls1, parts, D, m->top_w,
@@ -393,7 +412,7 @@ int enqueue_step(zl_dizizen* m, int T, int n_want, int n_runs, int max_run, int 
         ZL_CHECK_CUDA(launch(k_gather_rows_f32, dim3(n_want), dim3(128), 0, st, false, (const float*)m->x,
                              (const int32_t*)m->d_want, m->xw, D));
         RCHECK(zl_group_rmsnorm(m->xw, D, m->final_norm, m->xn, D, n_want, D, 1, c.eps, dt, pt, st));
-        RCHECK(linear(m, m->xn, D, m->head, c.vocab, nullptr, nullptr, m->logits, n_want, ZL_F32, ZL_GEMM_EPI_NONE));
+        RCHECK(linear(m, st, m->xn, D, m->head, c.vocab, nullptr, nullptr, m->logits, n_want, ZL_F32, ZL_GEMM_EPI_NONE));
         RCHECK(zl_argmax(m->logits, m->d_next, n_want, c.vocab, m->argmax_ws, zl_argmax_workspace_bytes(n_want), pt, st));
     }
     return ZL_OK;
@@ -466,6 +485,16 @@ extern "C" int zl_dizizen_create(const zl_dizizen_config_t* cfg, const zl_dizize
         zl_set_last_error(__FILE__, __LINE__, "cudaStreamCreate failed (no CUDA device? there is no CPU fallback)");
         return ZL_ERR_CUDA;
     }
+    bool ok = cudaStreamCreateWithFlags(&m->side, cudaStreamNonBlocking) == cudaSuccess;
+    for (auto* evs : {&m->ev_h, &m->ev_proj, &m->ev_ff}) {
+        evs->assign(cfg->num_layers, nullptr);
+        for (auto& e : *evs) ok = ok && cudaEventCreateWithFlags(&e, cudaEventDisableTiming) == cudaSuccess;
+    }
+    if (!ok) {
+        zl_dizizen_destroy(m);
+        zl_set_last_error(__FILE__, __LINE__, "creating the side stream or its events failed");
+        return ZL_ERR_CUDA;
+    }
     *out = m;
     return ZL_OK;
 }
@@ -473,6 +502,10 @@ extern "C" int zl_dizizen_create(const zl_dizizen_config_t* cfg, const zl_dizize
 extern "C" void zl_dizizen_destroy(zl_dizizen_t* m) {
     if (!m) return;
     cudaStreamSynchronize(m->stream);
+    if (m->side) cudaStreamSynchronize(m->side);
+    for (auto* evs : {&m->ev_h, &m->ev_proj, &m->ev_ff})
+        for (auto e : *evs)
+            if (e) cudaEventDestroy(e);
     for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
     for (auto& s : m->staged) cudaFree(s.second.ptr);
     for (auto& L : m->layers) {
@@ -493,6 +526,7 @@ extern "C" void zl_dizizen_destroy(zl_dizizen_t* m) {
                     (void*)m->list_pair, m->attn_ws, m->argmax_ws, (void*)m->layer_dump})
         if (p) cudaFree(p);
     if (m->h_stage) cudaFreeHost(m->h_stage);
+    if (m->side) cudaStreamDestroy(m->side);
     cudaStreamDestroy(m->stream);
     delete m;
 }
