@@ -699,7 +699,7 @@ def _dizizen_config(sz):
     att = dict(heads=sz["heads"], kv_heads=8, dim=sz["dim"], vdim=sz["dim"], scale=sz["dim"] ** -0.5,
                rot={"base": 5e5, "dims": sz["dim"] // 2})
     moe = {"kind": "moe", "expert": {"ff": sz["ff_e"]}, "shared": {"ff": 2 * sz["ff_e"]},
-           "router": {"experts": sz["experts"], "identity": 4, "top": sz["top"], "groups": {"count": 4, "keep": 3}}}
+           "router": {"experts": sz["experts"], "identity": 2, "top": sz["top"], "groups": {"count": 6, "keep": 4}}}
     dense = {"kind": "dense", "ff": sz["ff"], "limit": 7.0}
     layers = []
     for i in range(sz["layers"]):
@@ -716,7 +716,7 @@ def _dizizen_params(sz, rows):
     cache bytes per cached position)."""
     D, H, d = sz["width"], sz["heads"], sz["dim"]
     E, top, fe, F = sz["experts"], sz["top"], sz["ff_e"], sz["ff"]
-    slots = E + 4
+    slots = E + 2
     touched = E * (1.0 - (1.0 - top / slots) ** rows)   # expected number of distinct experts a step reads
     active = read = cache = 0
     for i in range(sz["layers"]):
