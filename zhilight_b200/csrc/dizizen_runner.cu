@@ -197,11 +197,14 @@ int finalize_layer(zl_dizizen* m, int l) {
     L.q_off = 0;
     L.k_off = own ? H * d : -1;
     L.v_off = own ? H * d + G * d : 0;
-    L.g1_off = H * d + (own ? G * (d + vd) : 0);
+    // the gates' columns start at a multiple of 4 and the row has a multiple of 8 columns (rows of zeros in between), so that
+    // the combine kernel reads its logits in 16-byte pieces whatever the head and slot counts are
+    L.g1_off = (H * d + (own ? G * (d + vd) : 0) + 3) & ~3;
     L.g2_off = ff ? L.g1_off + D : -1;
     L.r_off = moe ? L.g1_off + 2 * D : -1;
-    L.n_in = L.g1_off + D + (ff ? D : 0) + (moe ? slots : 0);
+    L.n_in = (L.g1_off + D + (ff ? D : 0) + (moe ? slots : 0) + 7) & ~7;
     RCHECK(dmalloc(&L.w_in, (size_t)L.n_in * D * m->esz));
+    ZL_CHECK_CUDA(cudaMemsetAsync(L.w_in, 0, (size_t)L.n_in * D * m->esz, m->stream));
     RCHECK(dmalloc((void**)&L.b_in, (size_t)L.n_in * 4));
     ZL_CHECK_CUDA(cudaMemsetAsync(L.b_in, 0, (size_t)L.n_in * 4, m->stream));
     RCHECK(put_weight(m, mx + "q", H * d, D, L.w_in, 0));
