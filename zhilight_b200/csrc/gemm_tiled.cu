@@ -307,9 +307,10 @@ static cudaError_t launch_small_m(const GemmP& p, int batch, int epi, bool pdl, 
 }
 
 // ---- grouped problems with few rows each (decode steps of a mixture of experts) ----------------------------------------
-// One CTA = 8 output columns of one group, one per warp; the group's rows (gathered through x_rows) sit in shared memory eight at a
-// time, and a warp streams the weight row of a column -- for the gated unit the gate and the up row of the column -- once
-// per eight rows with four 16-byte loads per row in flight.  Groups without rows cost an early exit.
+// One CTA = 8 output columns of one group with the gated unit, 16 without, one or two per warp; the group's rows (gathered
+// through x_rows) sit in shared memory eight at a time, and a warp streams two weight rows at once -- the gate and the up
+// row of its column, or the rows of its two columns -- once per eight rows with four 16-byte loads per row in flight.
+// Groups without rows cost an early exit.
 constexpr int kGrpCols = 8;
 
 template <typename T, typename TO, bool GLU>
@@ -322,6 +323,11 @@ __global__ void __launch_bounds__(256) k_gemm_grouped_small(GemmP p) {
     const T* x = static_cast<const T*>(p.x);
     TO* y = static_cast<TO*>(p.y);
     const int K = p.K, K8 = K / 8, n_out = GLU ? p.N / 2 : p.N;
+    // a warp streams two weight rows at once: gate and up of its column (gated unit), or the rows of two columns
+    // (8 apart) otherwise, so that eight 16-byte loads per lane are in flight either way
+    constexpr int kCols = GLU ? kGrpCols : 2 * kGrpCols;
+    const int n = blockIdx.x * kCols + warp, n2 = GLU ? n : n + kGrpCols;
+    const bool has1 = n < n_out, has2 = GLU ? has1 : n2 < n_out;
     pdl_wait();
     int M, first;
     gemm_rows_of(p, b, M, first);
@@ -334,66 +340,70 @@ __global__ void __launch_bounds__(256) k_gemm_grouped_small(GemmP p) {
             *reinterpret_cast<uint4*>(sx + (size_t)m * K + k8 * 8) = *reinterpret_cast<const uint4*>(x + row * p.ldx + k8 * 8);
         }
         __syncthreads();
-        for (int n = blockIdx.x * kGrpCols + warp; n < min(n_out, (int)(blockIdx.x + 1) * kGrpCols); n += 8) {
-            float acc[8], acc2[8];
+        if (!has1) continue;
+        float acc[8], acc2[8];
 #pragma unroll
-            for (int m = 0; m < 8; ++m) acc[m] = acc2[m] = 0.f;
-            const T* wr = w + (size_t)(GLU ? 2 * n : n) * p.ldw;
-            for (int k8 = lane; k8 < K8; k8 += 128) {
-                uint4 wq[4], wq2[4];
+        for (int m = 0; m < 8; ++m) acc[m] = acc2[m] = 0.f;
+        const T* wr = w + (size_t)(GLU ? 2 * n : n) * p.ldw;
+        const T* wr2 = GLU ? wr + p.ldw : w + (size_t)(has2 ? n2 : n) * p.ldw;
+        for (int k8 = lane; k8 < K8; k8 += 128) {
+            uint4 wq[4], wq2[4];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const bool in = k8 + 32 * u < K8;
-                    wq[u] = in ? ld_nc_na_u4(wr + (size_t)(k8 + 32 * u) * 8) : make_uint4(0, 0, 0, 0);
-                    if (GLU) wq2[u] = in ? ld_nc_na_u4(wr + p.ldw + (size_t)(k8 + 32 * u) * 8) : make_uint4(0, 0, 0, 0);
-                }
+            for (int u = 0; u < 4; ++u) {
+                const bool in = k8 + 32 * u < K8;
+                wq[u] = in ? ld_nc_na_u4(wr + (size_t)(k8 + 32 * u) * 8) : make_uint4(0, 0, 0, 0);
+                wq2[u] = (in && has2) ? ld_nc_na_u4(wr2 + (size_t)(k8 + 32 * u) * 8) : make_uint4(0, 0, 0, 0);
+            }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    if (k8 + 32 * u >= K8) break;
-                    float wf[8], wf2[8];
-                    unpack8<T>(wq[u], wf);
-                    if (GLU) unpack8<T>(wq2[u], wf2);
+            for (int u = 0; u < 4; ++u) {
+                if (k8 + 32 * u >= K8) break;
+                float wf[8], wf2[8];
+                unpack8<T>(wq[u], wf);
+                unpack8<T>(wq2[u], wf2);
 #pragma unroll
-                    for (int m = 0; m < 8; ++m) {
-                        if (m < mc) {
-                            float xf[8];
-                            unpack8<T>(*reinterpret_cast<const uint4*>(sx + (size_t)m * K + (size_t)(k8 + 32 * u) * 8), xf);
+                for (int m = 0; m < 8; ++m) {
+                    if (m < mc) {
+                        float xf[8];
+                        unpack8<T>(*reinterpret_cast<const uint4*>(sx + (size_t)m * K + (size_t)(k8 + 32 * u) * 8), xf);
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) {
-                                acc[m] = fmaf(wf[e], xf[e], acc[m]);
-                                if (GLU) acc2[m] = fmaf(wf2[e], xf[e], acc2[m]);
-                            }
+                        for (int e = 0; e < 8; ++e) {
+                            acc[m] = fmaf(wf[e], xf[e], acc[m]);
+                            acc2[m] = fmaf(wf2[e], xf[e], acc2[m]);
                         }
                     }
                 }
             }
-            float mine = 0.f;
+        }
+        float mine = 0.f, mine2 = 0.f;
 #pragma unroll
-            for (int m = 0; m < 8; ++m) {
-                float v = warp_sum(acc[m]);
-                if (GLU) {
-                    float v2 = warp_sum(acc2[m]);
-                    if (p.bias) v += p.bias[(size_t)b * p.bb + 2 * n], v2 += p.bias[(size_t)b * p.bb + 2 * n + 1];
-                    v = p.pair_gelu ? gelu_f(v) * v2 : glu_clamp(v, v2, p);
-                } else {
-                    if (p.bias) v += p.bias[(size_t)b * p.bb + n];
-                    if (p.act_tanh) v = tanhf(v);
-                    if (p.act_relu2) v = fmaxf(v, 0.f), v *= v;
-                    if (p.act_gelu_mul && m < mc) v = gelu_f(v) * p.gate[(size_t)(first + m0 + m) * p.ldg + n];
+        for (int m = 0; m < 8; ++m) {
+            float v = warp_sum(acc[m]), v2 = warp_sum(acc2[m]);
+            if (GLU) {
+                if (p.bias) v += p.bias[(size_t)b * p.bb + 2 * n], v2 += p.bias[(size_t)b * p.bb + 2 * n + 1];
+                v = p.pair_gelu ? gelu_f(v) * v2 : glu_clamp(v, v2, p);
+            } else {
+                if (p.bias) v += p.bias[(size_t)b * p.bb + n], v2 += has2 ? p.bias[(size_t)b * p.bb + n2] : 0.f;
+                if (p.act_tanh) v = tanhf(v), v2 = tanhf(v2);
+                if (p.act_relu2) v = fmaxf(v, 0.f), v *= v, v2 = fmaxf(v2, 0.f), v2 *= v2;
+                if (p.act_gelu_mul && m < mc) {
+                    const float* gr = p.gate + (size_t)(first + m0 + m) * p.ldg;
+                    v = gelu_f(v) * gr[n];
+                    v2 = has2 ? gelu_f(v2) * gr[n2] : 0.f;
                 }
-                if (lane == m) mine = v;
             }
-            if (lane < mc) {
-                const size_t yr = (size_t)(p.y_rows ? p.y_rows[first + m0 + lane] : first + m0 + lane) * p.ldy;
-                y[yr + n] = from_f32<TO>(mine);
-            }
+            if (lane == m) mine = v, mine2 = v2;
+        }
+        if (lane < mc) {
+            const size_t yr = (size_t)(p.y_rows ? p.y_rows[first + m0 + lane] : first + m0 + lane) * p.ldy;
+            y[yr + n] = from_f32<TO>(mine);
+            if (!GLU && has2) y[yr + n2] = from_f32<TO>(mine2);
         }
     }
 }
 
 template <typename T, typename TO>
 static cudaError_t launch_grouped_small(const GemmP& p, int groups, bool glu, bool pdl, cudaStream_t st) {
-    const dim3 grid(cdiv(glu ? p.N / 2 : p.N, kGrpCols), groups), block(256);
+    const dim3 grid(glu ? cdiv(p.N / 2, kGrpCols) : cdiv(p.N, 2 * kGrpCols), groups), block(256);
     const size_t smem = (size_t)8 * p.K * sizeof(T);
     cudaError_t e = cudaSuccess;
     static size_t set_glu = 0, set_plain = 0;
